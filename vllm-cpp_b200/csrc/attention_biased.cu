@@ -202,6 +202,94 @@ VCB_EXPORT int vcb_qk_norm_cache_write(const void* proj, long long ld, int q_off
     return vcb_last_error();
 }
 
+// ------------------------------------------------------------- norm per head, rotation, cache write
+// Queries and keys RMS-normed head by head over dk with one gain vector that all heads share (wq, wk: float [dk] or
+// null), then rotated on their first `rot` coordinates: coordinate i pairs with i + rot / 2, angle = position *
+// inv_freq[i] in float.  Keys and values go into the token's slot of the cache, queries to q_out.  A warp per head.
+struct QkHeadArgs {
+    QkNormArgs base;
+    const float* inv_freq;      // [rot / 2] or null
+    int rot;
+};
+
+template <typename T>
+__global__ void qk_head_rope_cache_write_kernel(QkHeadArgs h) {
+    const QkNormArgs& a = h.base;
+    pdl_start();
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const T* src = (const T*)a.proj + (size_t)t * a.ld;
+    const int pos = a.positions[t];
+    const int half = h.rot >> 1;
+    T* kp = nullptr;
+    T* vp = nullptr;
+    const size_t block = (size_t)a.page * a.row;
+    int slot = 0;
+    if (a.write_kv) {
+        const int lp = pos / a.page;
+        slot = pos - lp * a.page;
+        const int pg = lp < a.bt_stride ? a.block_table[(size_t)a.req_of_token[t] * a.bt_stride + lp] : -1;
+        if ((unsigned)pg >= (unsigned)a.num_pages) {
+            if (a.status && threadIdx.x == 0) atomicCAS(a.status, 0, VCB_STATUS_BAD_PAGE);
+        } else {
+            kp = (T*)a.cache + (size_t)pg * 2 * a.G * block;
+            vp = kp + (size_t)a.G * block;
+        }
+    }
+    for (int head = warp; head < a.H + a.G; head += nwarps) {
+        const bool is_q = head < a.H;
+        const int g = is_q ? head : head - a.H;
+        const T* x = src + (is_q ? a.q_off + g * a.dk : a.k_off + g * a.dk);
+        const float* w = is_q ? a.wq : a.wk;
+        float r = 1.0f;
+        if (w) {
+            float ss = 0.0f;
+            for (int i = lane; i < a.dk; i += 32) { const float v = to_f32<T>(x[i]); ss = fmaf(v, v, ss); }
+            r = 1.0f / sqrtf(warp_sum(ss) / (float)a.dk + a.eps);
+        }
+        if (!is_q && !kp) continue;
+        T* qo = (T*)a.q_out + (size_t)t * a.H * a.dk + (size_t)g * a.dk;
+        T* ko = is_q ? nullptr : kp + (size_t)g * block;
+        for (int i = lane; i < a.dk; i += 32) {
+            float v = to_f32<T>(x[i]) * r * (w ? w[i] : 1.0f);
+            if (i < h.rot) {
+                const int j = i < half ? i : i - half, partner = i < half ? i + half : i - half;
+                const float pv = to_f32<T>(x[partner]) * r * (w ? w[partner] : 1.0f);
+                float sn, cs;
+                sincosf((float)pos * h.inv_freq[j], &sn, &cs);
+                v = i < half ? v * cs - pv * sn : v * cs + pv * sn;
+            }
+            if (is_q) qo[i] = from_f32<T>(v);
+            else ko[kv_pos(i, slot, a.row, a.page, (int)sizeof(T))] = from_f32<T>(v);
+        }
+    }
+    if (!vp) return;
+    const int nv = a.G * a.dv;
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+        const int g = i / a.dv, c = i - g * a.dv;
+        vp[g * block + kv_pos(c, slot, a.row, a.page, (int)sizeof(T))] = src[a.v_off + i];
+    }
+}
+
+VCB_EXPORT int vcb_qk_head_rope_cache_write(const void* proj, long long ld, int q_off, int k_off, int v_off, const float* wq,
+                                            const float* wk, const float* inv_freq, int rot, void* q_out, void* cache,
+                                            const int* positions, const int* req_of_token, const int* block_table,
+                                            int bt_stride, int n_tokens, int H, int G, int dk, int dv, int row, int page,
+                                            int num_pages, int write_kv, float eps, int* status, int dtype, void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (!proj || !q_out || !cache || H <= 0 || G <= 0 || dk <= 0 || dv <= 0 || row < dk || row < dv || page <= 0 || rot < 0 ||
+        rot > dk || (rot & 1) || (rot && !inv_freq))
+        return VCB_ERR_BAD_ARG;
+    QkHeadArgs a{{proj, ld, q_off, k_off, v_off, wq, wk, q_out, cache, positions, req_of_token, block_table, bt_stride,
+                  H, G, dk, dv, row, page, num_pages, write_kv, eps, status}, inv_freq, rot};
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = (H + G) >= 8 ? 256 : 128;
+    if (dtype == VCB_F32) vcb_launch(qk_head_rope_cache_write_kernel<float>, n_tokens, threads, 0, s, a);
+    else if (dtype == VCB_BF16) vcb_launch(qk_head_rope_cache_write_kernel<__nv_bfloat16>, n_tokens, threads, 0, s, a);
+    else return VCB_ERR_BAD_ARG;
+    return vcb_last_error();
+}
+
 // ---------------------------------------------------------------------------------------- attention
 #define ATB_MAX_DV 256
 #define ATB_WARPS 4
@@ -221,6 +309,8 @@ struct BiasedAttnArgs {
     float scale, cap;           // cap <= 0: scores are not capped
     int num_pages;
     int* status;
+    const float* sink;          // [nh] or null: a logit per head that joins the softmax's denominator and has no value
+    int gate_per_head;          // 1: the gate holds one number per head ([n, nh]) instead of one per channel
 };
 
 template <typename T>
@@ -295,14 +385,22 @@ __global__ void attention_biased_kernel(BiasedAttnArgs a) {
         m = m_new;
     }
     T* orow = (T*)a.out + ((size_t)t * a.nh + h) * a.dv;
-    const T* grow = a.gate ? (const T*)a.gate + (size_t)t * a.ldg + (size_t)h * a.dv : nullptr;
-    const float inv = 1.0f / l;
+    const T* grow = a.gate ? (const T*)a.gate + (size_t)t * a.ldg + (a.gate_per_head ? (size_t)h : (size_t)h * a.dv) : nullptr;
+    float keep = 1.0f;
+    if (a.sink) {
+        // the sink counts once in the denominator, unscaled; the reference of the exponents moves if it is the largest
+        const float sk = a.sink[h], mf = fmaxf(m, sk);
+        keep = expf(m - mf);
+        l = l * keep + expf(sk - mf);
+    }
+    const float inv = keep / l;
+    const float head_gate = (grow && a.gate_per_head) ? 1.0f / (1.0f + expf(-to_f32<T>(grow[0]))) : 1.0f;
 #pragma unroll
     for (int k = 0; k < ATB_MAX_DV / 32; ++k) {
         const int dim = lane + 32 * k;
         if (dim < a.dv) {
-            float y = o[k] * inv;
-            if (grow) y *= 1.0f / (1.0f + expf(-to_f32<T>(grow[dim])));
+            float y = o[k] * inv * head_gate;
+            if (grow && !a.gate_per_head) y *= 1.0f / (1.0f + expf(-to_f32<T>(grow[dim])));
             orow[dim] = from_f32<T>(y);
         }
     }
@@ -311,14 +409,14 @@ __global__ void attention_biased_kernel(BiasedAttnArgs a) {
 VCB_EXPORT int vcb_attention_biased(const void* q, const void* cache, void* out, const void* gate, long long ldg,
                                     const int* positions, const int* req_of_token, const int* block_table, int bt_stride,
                                     const float* bias, int bias_len, int n_tokens, int nh, int nkv, int dk, int dv, int row,
-                                    int page, int window, float scale, float cap, int num_pages, int* status, int dtype,
-                                    void* stream) {
+                                    int page, int window, float scale, float cap, int num_pages, int* status,
+                                    const float* sink, int gate_per_head, int dtype, void* stream) {
     if (n_tokens <= 0) return 0;
     if (dk <= 0 || dv <= 0 || dv > ATB_MAX_DV || dk > 1024 || row < dk || row < dv || nh <= 0 || nkv <= 0 || nh % nkv ||
         page <= 0 || window < 0 || num_pages < 0 || (bias && bias_len <= 0))
         return VCB_ERR_BAD_ARG;
     BiasedAttnArgs a{q, cache, out, gate, ldg, positions, req_of_token, block_table, bias, bias_len, bt_stride, n_tokens,
-                     nh, nkv, dk, dv, row, page, window, scale, cap, num_pages, status};
+                     nh, nkv, dk, dv, row, page, window, scale, cap, num_pages, status, sink, gate_per_head};
     const long long items = (long long)n_tokens * nh;
     const int blocks = (int)((items + ATB_WARPS - 1) / ATB_WARPS);
     const size_t smem = (size_t)ATB_WARPS * dk * sizeof(float);

@@ -1,0 +1,435 @@
+// Recurrent mixers whose inputs pass a short causal convolution first, and their recurrences:
+//
+//   causal_conv_kernel        y[t, c] = act(sum_j w[c, j] x[t - (J - 1) + j, c] + b[c]) over the tokens of a request, the
+//                             J - 1 inputs before a step's first token read from the request's state slot (zero at
+//                             admission, which is "zeros before the start") and the step's last J - 1 inputs left there
+//   gate_blocks_kernel        the gates of a real-gated linear recurrent unit from block-diagonal products of the
+//                             convolved branch u:  r = sigmoid(Wa_b u_b + ba), i = sigmoid(Wi_b u_b + bi),
+//                             log a = -c r softplus(lam), and what the recurrence adds, sqrt(1 - a^2) i u
+//   linear_recurrence_kernel  S_t = a_t S_(t-1) + b_t per channel from the state slot, result S_t * gelu_tanh(y_t + by)
+//   gated_delta_scan_kernel   the gated delta rule per head on a matrix S [dk, dv]:
+//                                 S <- diag(g_t) S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t
+//                             with q and k made unit vectors here, g_t = exp(-exp(A) softplus(z_t + dt_bias)) per key
+//                             channel and beta_t = sigmoid(.)
+//
+// States, decays and their logarithms, softplus and exponentials, gates, unit norms and every sum are float whatever the
+// type T of the projections is.  The reference has no recurrent mixer (src/layers/attention.cpp is its only mixer).
+#include "common.cuh"
+
+#define CONV_MAX_TAPS 8
+#define CONV_SEG 32            // tokens a thread walks; at least CONV_MAX_TAPS - 1, so that only a request's first segment reads the state
+
+__device__ __forceinline__ float gr_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float gr_silu(float z) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ float gr_softplus(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
+__device__ __forceinline__ float gr_gelu_tanh(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+struct ConvArgs {
+    const void* x;              // [n, C] rows of T, row stride ldx
+    long long ldx;
+    const float* pre_bias;      // [C] or null: added to every input (never to the zeros before the start)
+    const float* w;             // [C, J]
+    const float* bias;          // [C] or null: added to the sum
+    float* state;               // slot s, row j (0 .. J - 2), channel c at state[s * slot_stride + j * C + c]
+    long long slot_stride;
+    float* out;                 // [n, C] float, row stride ldo
+    long long ldo;
+    const int* q_start;
+    const int* state_slots;
+    int C, J, act;
+};
+
+// Grid (segments of the longest portion, requests, tiles of 128 channels); a thread per channel.
+template <typename T>
+__global__ void __launch_bounds__(128) causal_conv_kernel(ConvArgs a) {
+    const int c = blockIdx.z * 128 + threadIdx.x;
+    float w[CONV_MAX_TAPS];
+    const int J = a.J;
+    const bool live = c < a.C;
+#pragma unroll
+    for (int j = 0; j < CONV_MAX_TAPS; ++j) w[j] = (live && j < J) ? a.w[(size_t)c * J + j] : 0.0f;
+    const float pb = (live && a.pre_bias) ? a.pre_bias[c] : 0.0f, cb = (live && a.bias) ? a.bias[c] : 0.0f;
+    pdl_start();
+    const int r = blockIdx.y;
+    const int row0 = a.q_start[r], len = a.q_start[r + 1] - row0;
+    const int seg0 = blockIdx.x * CONV_SEG;
+    if (seg0 >= len || !live) return;
+    const T* x = (const T*)a.x + (size_t)row0 * a.ldx + c;
+    float* st = a.state + (size_t)a.state_slots[r] * a.slot_stride + c;
+    // win[j]: the input J - 1 - j places before the current token, oldest first
+    float win[CONV_MAX_TAPS - 1], old[CONV_MAX_TAPS - 1];
+#pragma unroll
+    for (int j = 0; j < CONV_MAX_TAPS - 1; ++j) {
+        win[j] = old[j] = 0.0f;
+        if (j < J - 1) {
+            const int li = seg0 - (J - 1) + j;
+            win[j] = li >= 0 ? to_f32<T>(x[(size_t)li * a.ldx]) + pb : st[(size_t)(J - 1 + li) * a.C];
+            old[j] = win[j];
+        }
+    }
+    const int end = min(seg0 + CONV_SEG, len);
+    float* out = a.out + (size_t)row0 * a.ldo + c;
+    for (int t = seg0; t < end; ++t) {
+        const float cur = to_f32<T>(x[(size_t)t * a.ldx]) + pb;
+        float acc = cb;
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS - 1; ++j)
+            if (j < J - 1) acc = fmaf(w[j], win[j], acc);
+        acc = fmaf(w[J - 1], cur, acc);
+        out[(size_t)t * a.ldo] = a.act ? gr_silu(acc) : acc;
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS - 2; ++j) win[j] = win[j + 1];
+        if (J >= 2) {
+#pragma unroll
+            for (int j = 0; j < CONV_MAX_TAPS - 1; ++j)
+                if (j == J - 2) win[j] = cur;
+        }
+    }
+    if (seg0 == 0) {
+        // this thread alone reads and writes the channel's state: what it read is in old[]
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS - 1; ++j) {
+            if (j >= J - 1) break;
+            const int li = len - (J - 1) + j;
+            st[(size_t)j * a.C] = li >= 0 ? to_f32<T>(x[(size_t)li * a.ldx]) + pb : old[J - 1 + li];
+        }
+    }
+}
+
+VCB_EXPORT int vcb_causal_conv(const void* x, long long ldx, const float* pre_bias, const float* w, const float* bias,
+                               float* state, long long slot_stride, float* out, long long ldo, const int* q_start,
+                               const int* state_slots, int n_reqs, int max_q_len, int C, int J, int act, int dtype,
+                               void* stream) {
+    if (n_reqs <= 0 || max_q_len <= 0) return 0;
+    if (!x || !w || !state || !out || C <= 0 || J <= 0 || J > CONV_MAX_TAPS || n_reqs > 65535) return VCB_ERR_BAD_ARG;
+    ConvArgs a{x, ldx, pre_bias, w, bias, state, slot_stride, out, ldo, q_start, state_slots, C, J, act};
+    dim3 grid((max_q_len + CONV_SEG - 1) / CONV_SEG, n_reqs, (C + 127) / 128);
+    if (grid.z > 65535) return VCB_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == VCB_F32) vcb_launch(causal_conv_kernel<float>, grid, 128, 0, s, a);
+    else if (dtype == VCB_BF16) vcb_launch(causal_conv_kernel<__nv_bfloat16>, grid, 128, 0, s, a);
+    else return VCB_ERR_BAD_ARG;
+    return vcb_last_error();
+}
+
+// ------------------------------------------------------------------------------- gates of the recurrent unit
+// u: float [n, W]; W = B blocks of bs channels; wa, wi: [B, bs, bs] of T ([out, in]); ba, bi: float [W]; lam: float [W].
+// decay[t, c] = exp(-c_gate * r * softplus(lam[c])),  drive[t, c] = sqrt(1 - decay^2) * i * u[t, c].
+// A CTA owns 64 tokens x 64 channels of one block; 16-deep slices of the block's inputs through shared memory; float FMA.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gate_blocks_kernel(const float* __restrict__ u, long long ldu, const T* __restrict__ wa, const T* __restrict__ wi,
+                   const float* __restrict__ ba, const float* __restrict__ bi, const float* __restrict__ lam,
+                   float* __restrict__ decay, float* __restrict__ drive, long long ldo, int n, int bs, int tiles_per_block,
+                   float c_gate) {
+    __shared__ float Us[16][64 + 1];
+    __shared__ float As[16][64 + 1];
+    __shared__ float Is[16][64 + 1];
+    pdl_start();
+    const int b = blockIdx.y / tiles_per_block, n0 = (blockIdx.y % tiles_per_block) * 64;
+    const int t0 = blockIdx.x * 64;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const T* Wa = wa + (size_t)b * bs * bs;
+    const T* Wi = wi + (size_t)b * bs * bs;
+    const float* ub = u + (size_t)b * bs;
+    float accr[4][4], acci[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) accr[i][j] = acci[i][j] = 0.0f;
+    for (int k0 = 0; k0 < bs; k0 += 16) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int idx = threadIdx.x + q * 256;
+            const int r = idx >> 4, kk = idx & 15, k = k0 + kk;
+            Us[kk][r] = (t0 + r < n && k < bs) ? ub[(size_t)(t0 + r) * ldu + k] : 0.0f;
+            const bool ok = n0 + r < bs && k < bs;
+            As[kk][r] = ok ? to_f32<T>(Wa[(size_t)(n0 + r) * bs + k]) : 0.0f;
+            Is[kk][r] = ok ? to_f32<T>(Wi[(size_t)(n0 + r) * bs + k]) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < 16; ++kk) {
+            float uv[4], av[4], iv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) uv[i] = Us[kk][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { av[j] = As[kk][tx * 4 + j]; iv[j] = Is[kk][tx * 4 + j]; }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    accr[i][j] = fmaf(uv[i], av[j], accr[i][j]);
+                    acci[i][j] = fmaf(uv[i], iv[j], acci[i][j]);
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int t = t0 + ty * 4 + i;
+        if (t >= n) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int cb = n0 + tx * 4 + j;
+            if (cb >= bs) continue;
+            const int c = b * bs + cb;
+            const float r = gr_sigmoid(accr[i][j] + ba[c]), g = gr_sigmoid(acci[i][j] + bi[c]);
+            const float la = -c_gate * r * gr_softplus(lam[c]);
+            decay[(size_t)t * ldo + c] = expf(la);
+            drive[(size_t)t * ldo + c] = sqrtf(-expm1f(2.0f * la)) * g * u[(size_t)t * ldu + c];
+        }
+    }
+}
+
+VCB_EXPORT int vcb_gate_blocks(const float* u, long long ldu, const void* wa, const void* wi, const float* ba, const float* bi,
+                               const float* lam, float* decay, float* drive, long long ldo, int n, int W, int B, float c_gate,
+                               int dtype, void* stream) {
+    if (n <= 0) return 0;
+    if (!u || !wa || !wi || !ba || !bi || !lam || !decay || !drive || W <= 0 || B <= 0 || W % B) return VCB_ERR_BAD_ARG;
+    const int bs = W / B, tiles = (bs + 63) / 64;
+    if ((long long)B * tiles > 65535) return VCB_ERR_UNSUPPORTED;
+    dim3 grid((n + 63) / 64, B * tiles);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == VCB_F32)
+        vcb_launch(gate_blocks_kernel<float>, grid, 256, 0, s, u, ldu, (const float*)wa, (const float*)wi, ba, bi, lam, decay, drive, ldo, n, bs, tiles, c_gate);
+    else if (dtype == VCB_BF16)
+        vcb_launch(gate_blocks_kernel<__nv_bfloat16>, grid, 256, 0, s, u, ldu, (const __nv_bfloat16*)wa, (const __nv_bfloat16*)wi, ba, bi, lam,
+                   decay, drive, ldo, n, bs, tiles, c_gate);
+    else return VCB_ERR_BAD_ARG;
+    return vcb_last_error();
+}
+
+// ------------------------------------------------------------------------------- S_t = a_t S_(t-1) + b_t
+// decay, drive: float [n, W]; y: [n, W] rows of T (row stride ldy) with bias by (float [W] or null); state: slot s,
+// channel c at state[s * slot_stride + c]; out [n, W] of T = S_t * gelu_tanh(y_t + by).  A thread per channel walks
+// its request's tokens, four tokens' loads in flight.
+template <typename T>
+__global__ void __launch_bounds__(128)
+linear_recurrence_kernel(const float* __restrict__ decay, const float* __restrict__ drive, long long ldd, const T* __restrict__ y,
+                         long long ldy, const float* __restrict__ by, float* __restrict__ state, long long slot_stride,
+                         T* __restrict__ out, long long ldo, const int* __restrict__ q_start, const int* __restrict__ state_slots,
+                         int W) {
+    const int c = blockIdx.y * 128 + threadIdx.x;
+    const float yb = (c < W && by) ? by[c] : 0.0f;
+    pdl_start();
+    if (c >= W) return;
+    const int r = blockIdx.x;
+    const int row0 = q_start[r], row1 = q_start[r + 1];
+    float* st = state + (size_t)state_slots[r] * slot_stride + c;
+    float S = *st;
+    int t = row0;
+    for (; t + 4 <= row1; t += 4) {
+        float a[4], b[4], g[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            a[k] = decay[(size_t)(t + k) * ldd + c];
+            b[k] = drive[(size_t)(t + k) * ldd + c];
+            g[k] = to_f32<T>(y[(size_t)(t + k) * ldy + c]);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            S = fmaf(a[k], S, b[k]);
+            out[(size_t)(t + k) * ldo + c] = from_f32<T>(S * gr_gelu_tanh(g[k] + yb));
+        }
+    }
+    for (; t < row1; ++t) {
+        S = fmaf(decay[(size_t)t * ldd + c], S, drive[(size_t)t * ldd + c]);
+        out[(size_t)t * ldo + c] = from_f32<T>(S * gr_gelu_tanh(to_f32<T>(y[(size_t)t * ldy + c]) + yb));
+    }
+    *st = S;
+}
+
+VCB_EXPORT int vcb_linear_recurrence(const float* decay, const float* drive, long long ldd, const void* y, long long ldy,
+                                     const float* by, float* state, long long slot_stride, void* out, long long ldo,
+                                     const int* q_start, const int* state_slots, int n_reqs, int W, int dtype, void* stream) {
+    if (n_reqs <= 0) return 0;
+    if (!decay || !drive || !y || !state || !out || W <= 0 || (W + 127) / 128 > 65535) return VCB_ERR_BAD_ARG;
+    dim3 grid(n_reqs, (W + 127) / 128);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == VCB_F32)
+        vcb_launch(linear_recurrence_kernel<float>, grid, 128, 0, s, decay, drive, ldd, (const float*)y, ldy, by, state, slot_stride,
+                   (float*)out, ldo, q_start, state_slots, W);
+    else if (dtype == VCB_BF16)
+        vcb_launch(linear_recurrence_kernel<__nv_bfloat16>, grid, 128, 0, s, decay, drive, ldd, (const __nv_bfloat16*)y, ldy, by, state,
+                   slot_stride, (__nv_bfloat16*)out, ldo, q_start, state_slots, W);
+    else return VCB_ERR_BAD_ARG;
+    return vcb_last_error();
+}
+
+// ------------------------------------------------------------------------------- the gated delta rule
+struct DeltaArgs {
+    const float* q;             // [n, G * dk] float (convolved, activated), row stride ldq
+    const float* k;
+    const float* v;             // [n, H * dv], row stride ldv
+    long long ldq, ldk, ldv;
+    const void* beta_pre;       // [n, H] rows of T, row stride ldb: beta = sigmoid(.)
+    long long ldb;
+    const void* decay_pre;      // [n, H * dk] rows of T, row stride lda
+    long long lda;
+    const float* a_log;         // [H]
+    const float* dt_bias;       // [H * dk]
+    float* state;               // [slots][H][dk][dv]
+    float* out;                 // [n, H * dv] float, row stride ldo
+    long long ldo;
+    const int* q_start;
+    const int* state_slots;
+    int H, G, dk, dv;
+    float q_scale, unit_eps;
+    int chunk;                  // tokens staged in shared memory at a time
+};
+
+// Grid (request, head, tile of DVT value channels).  A thread keeps DKP rows of one column of S in registers; the P
+// threads that share a column are neighbouring lanes of a warp and add their partial sums up by shuffles, so a token
+// costs no block-wide barrier.  Key channels beyond dk are padded with q = k = 0, g = 1.
+template <typename T, int DKP>
+__global__ void gated_delta_scan_kernel(DeltaArgs a, int P, int DVT) {
+    extern __shared__ __align__(16) float sm[];
+    pdl_start();
+    const int r = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * DVT;
+    const int kvh = h / (a.H / a.G);
+    const int tid = threadIdx.x, nthreads = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarps = nthreads >> 5;
+    const int part = tid % P, cl = tid / P;
+    const int col = col0 + cl;
+    const bool col_ok = cl < DVT && col < a.dv;
+    const int TC = a.chunk;
+    const int pstride = DKP + 4;                  // a part's slice of a token's q, k, g; padded against bank conflicts
+    const int tstride = P * pstride;
+    float* qs = sm;
+    float* ks = qs + TC * tstride;
+    float* gs = ks + TC * tstride;
+    float* vs = gs + TC * tstride;                // [TC][DVT]
+    float* os = vs + TC * DVT;                    // [TC][DVT]
+    float* bs = os + TC * DVT;                    // [TC]
+    const int row0 = a.q_start[r], row1 = a.q_start[r + 1];
+    float* st = a.state + (((size_t)a.state_slots[r] * a.H + h) * a.dk) * a.dv;
+    float S[DKP];
+#pragma unroll
+    for (int i = 0; i < DKP; ++i) {
+        const int kr = part * DKP + i;
+        S[i] = (col_ok && kr < a.dk) ? st[(size_t)kr * a.dv + col] : 0.0f;
+    }
+    const float rate = expf(a.a_log[h]);
+    const T* bp = (const T*)a.beta_pre;
+    const T* dp = (const T*)a.decay_pre;
+    for (int c0 = row0; c0 < row1; c0 += TC) {
+        const int tc = min(TC, row1 - c0);
+        __syncthreads();                          // the chunk before has been read
+        // a warp per token: unit q and k, the decays, beta
+        for (int tt = warp; tt < tc; tt += nwarps) {
+            const size_t row = (size_t)(c0 + tt);
+            const float* qr = a.q + row * a.ldq + kvh * a.dk;
+            const float* kr = a.k + row * a.ldk + kvh * a.dk;
+            float sq = 0.0f, sk = 0.0f;
+            for (int i = lane; i < a.dk; i += 32) { const float x = qr[i], y = kr[i]; sq = fmaf(x, x, sq); sk = fmaf(y, y, sk); }
+            sq = warp_sum(sq);
+            sk = warp_sum(sk);
+            const float rq = a.q_scale / sqrtf(sq + a.unit_eps), rk = 1.0f / sqrtf(sk + a.unit_eps);
+            for (int i = lane; i < P * DKP; i += 32) {
+                const int p = i / DKP, j = i - p * DKP;
+                float qv = 0.0f, kv = 0.0f, gv = 1.0f;
+                if (i < a.dk) {
+                    qv = qr[i] * rq;
+                    kv = kr[i] * rk;
+                    const float z = to_f32<T>(dp[row * a.lda + h * a.dk + i]) + a.dt_bias[h * a.dk + i];
+                    gv = expf(-rate * gr_softplus(z));
+                }
+                const int at = tt * tstride + p * pstride + j;
+                qs[at] = qv;
+                ks[at] = kv;
+                gs[at] = gv;
+            }
+            if (lane == 0) bs[tt] = gr_sigmoid(to_f32<T>(bp[row * a.ldb + h]));
+        }
+        for (int idx = tid; idx < tc * DVT; idx += nthreads) {
+            const int tt = idx / DVT, j = idx - tt * DVT, c = col0 + j;
+            vs[idx] = c < a.dv ? a.v[(size_t)(c0 + tt) * a.ldv + h * a.dv + c] : 0.0f;
+        }
+        __syncthreads();
+        if (cl < DVT) {
+            for (int tt = 0; tt < tc; ++tt) {
+                const float4* qq = reinterpret_cast<const float4*>(qs + tt * tstride + part * pstride);
+                const float4* kk = reinterpret_cast<const float4*>(ks + tt * tstride + part * pstride);
+                const float4* gg = reinterpret_cast<const float4*>(gs + tt * tstride + part * pstride);
+                float p0 = 0.0f, p1 = 0.0f;
+#pragma unroll
+                for (int i = 0; i < DKP / 4; ++i) {
+                    const float4 g4 = gg[i], k4 = kk[i];
+                    S[4 * i] *= g4.x; S[4 * i + 1] *= g4.y; S[4 * i + 2] *= g4.z; S[4 * i + 3] *= g4.w;
+                    p0 = fmaf(S[4 * i], k4.x, p0);
+                    p1 = fmaf(S[4 * i + 1], k4.y, p1);
+                    p0 = fmaf(S[4 * i + 2], k4.z, p0);
+                    p1 = fmaf(S[4 * i + 3], k4.w, p1);
+                }
+                float p = p0 + p1;
+                for (int o = 1; o < P; o <<= 1) p += __shfl_xor_sync(0xffffffffu, p, o);
+                const float u = bs[tt] * (vs[tt * DVT + cl] - p);
+                float o0 = 0.0f, o1 = 0.0f;
+#pragma unroll
+                for (int i = 0; i < DKP / 4; ++i) {
+                    const float4 k4 = kk[i], q4 = qq[i];
+                    S[4 * i] = fmaf(k4.x, u, S[4 * i]);
+                    S[4 * i + 1] = fmaf(k4.y, u, S[4 * i + 1]);
+                    S[4 * i + 2] = fmaf(k4.z, u, S[4 * i + 2]);
+                    S[4 * i + 3] = fmaf(k4.w, u, S[4 * i + 3]);
+                    o0 = fmaf(S[4 * i], q4.x, o0);
+                    o1 = fmaf(S[4 * i + 1], q4.y, o1);
+                    o0 = fmaf(S[4 * i + 2], q4.z, o0);
+                    o1 = fmaf(S[4 * i + 3], q4.w, o1);
+                }
+                float o = o0 + o1;
+                for (int d = 1; d < P; d <<= 1) o += __shfl_xor_sync(0xffffffffu, o, d);
+                if (part == 0) os[tt * DVT + cl] = o;
+            }
+        }
+        __syncthreads();
+        for (int idx = tid; idx < tc * DVT; idx += nthreads) {
+            const int tt = idx / DVT, j = idx - tt * DVT, c = col0 + j;
+            if (c < a.dv) a.out[(size_t)(c0 + tt) * a.ldo + h * a.dv + c] = os[idx];
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < DKP; ++i) {
+        const int kr = part * DKP + i;
+        if (col_ok && kr < a.dk) st[(size_t)kr * a.dv + col] = S[i];
+    }
+}
+
+template <typename T>
+static int launch_delta(const DeltaArgs& a, int n_reqs, cudaStream_t s) {
+    const int dkp = a.dk <= 32 ? 8 : a.dk <= 64 ? 16 : 32;
+    int P = 1;
+    while (P * dkp < a.dk) P <<= 1;
+    if (P > 32) return VCB_ERR_UNSUPPORTED;
+    const int dvt = P <= 8 ? 32 : 256 / P;
+    const int threads = ((dvt * P + 31) / 32) * 32;
+    int chunk = 16;
+    auto bytes = [&](int tc) { return ((size_t)tc * (3 * P * (dkp + 4) + 2 * dvt + 1)) * sizeof(float); };
+    while (chunk > 1 && bytes(chunk) > 48 * 1024) chunk >>= 1;
+    DeltaArgs b = a;
+    b.chunk = chunk;
+    dim3 grid(n_reqs, a.H, (a.dv + dvt - 1) / dvt);
+    if (dkp == 8) vcb_launch(gated_delta_scan_kernel<T, 8>, grid, threads, bytes(chunk), s, b, P, dvt);
+    else if (dkp == 16) vcb_launch(gated_delta_scan_kernel<T, 16>, grid, threads, bytes(chunk), s, b, P, dvt);
+    else vcb_launch(gated_delta_scan_kernel<T, 32>, grid, threads, bytes(chunk), s, b, P, dvt);
+    return vcb_last_error();
+}
+
+VCB_EXPORT int vcb_gated_delta_scan(const float* q, const float* k, const float* v, long long ldq, long long ldk, long long ldv,
+                                    const void* beta_pre, long long ldb, const void* decay_pre, long long lda,
+                                    const float* a_log, const float* dt_bias, float* state, float* out, long long ldo,
+                                    const int* q_start, const int* state_slots, int n_reqs, int H, int G, int dk, int dv,
+                                    float q_scale, float unit_eps, int dtype, void* stream) {
+    if (n_reqs <= 0) return 0;
+    if (!q || !k || !v || !beta_pre || !decay_pre || !a_log || !dt_bias || !state || !out || H <= 0 || G <= 0 || H % G ||
+        dk <= 0 || dv <= 0 || H > 65535 || (dv + 7) / 8 > 65535)
+        return VCB_ERR_BAD_ARG;
+    DeltaArgs a{q, k, v, ldq, ldk, ldv, beta_pre, ldb, decay_pre, lda, a_log, dt_bias, state, out, ldo, q_start, state_slots,
+                H, G, dk, dv, q_scale, unit_eps, 0};
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == VCB_F32) return launch_delta<float>(a, n_reqs, s);
+    if (dtype == VCB_BF16) return launch_delta<__nv_bfloat16>(a, n_reqs, s);
+    return VCB_ERR_BAD_ARG;
+}

@@ -1,12 +1,15 @@
 // A feed-forward of many small experts of which every token uses a few, without the host in the loop:
 //
-//   moe_router_*_kernel      logits = W_r h in float, softmax over all router outputs, the `top` outputs with the
-//                            largest (score + correction) chosen, their plain scores kept as weights
+//   moe_router_*_kernel      logits = W_r h in float; scores by softmax over all router outputs or by a sigmoid each; the
+//                            `top` outputs with the largest (score + correction) chosen, optionally only among the best
+//                            groups of neighbouring outputs; their plain scores kept as weights, optionally divided by
+//                            their sum and scaled (RouteRule)
 //   moe_sort_kernel          the (token, choice) pairs grouped by expert: a row for each pair in a list sorted by
 //                            expert, and the list's tiles of up to TM rows of one expert
 //   moe_expert_gemm_kernel   one product per tile against that expert's matrix; the first product gathers the
 //                            tokens' rows, computes gate and up together and applies the experts' activation
-//                              g = min(gate, limit), u = clamp(up, -limit, limit), y = g * sigmoid(alpha * g) * (u + 1)
+//                              g = min(gate, limit), u = clamp(up, -limit, limit), y = g * sigmoid(alpha * g) * (u + up_shift)
+//                            (limit = inf, alpha = 1, up_shift = 0: silu(gate) * up)
 //   moe_combine_kernel       out[t] = sum over the token's choices of weight * (the expert's row, or h[t] itself for a
 //                            router output beyond the experts: an identity expert)
 //
@@ -79,28 +82,79 @@ moe_router_logits_kernel(const T* __restrict__ h, long long ldh, const float* __
     }
 }
 
+// How the scores are made and used (the fields a design does not have stay at their neutral values).
+struct RouteRule {
+    int score_fn;               // 0: softmax over all outputs; 1: sigmoid of each logit
+    int n_groups, keep_groups;  // outputs form n_groups equal groups of neighbours, only those of the keep_groups best may be chosen
+    int group_top;              // a group's score: the sum of its group_top largest (score + correction); at most 4
+    int normalize;              // 1: the chosen weights are divided by (their sum + sum_eps)
+    float sum_eps, scale;       // scale multiplies the weights
+};
+
 __global__ void __launch_bounds__(128)
 moe_router_select_kernel(const float* __restrict__ logits, const float* __restrict__ correction, int* __restrict__ ids,
-                         float* __restrict__ wts, int n_tokens, int n_out, int top) {
+                         float* __restrict__ wts, int n_tokens, int n_out, int top, RouteRule rule) {
     extern __shared__ float sm[];
     pdl_start();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * 4 + warp;
     if (t >= n_tokens) return;
-    float* score = sm + (size_t)warp * 2 * n_out;      // [n_out] scores
-    float* choice = score + n_out;                     // [n_out] score + correction; -inf once taken
+    float* score = sm + (size_t)warp * (2 * n_out + rule.n_groups);      // [n_out] scores
+    float* choice = score + n_out;                     // [n_out] score + correction; -inf once taken or shut out
+    float* gscore = choice + n_out;                    // [n_groups]
     const float* z = logits + (size_t)t * n_out;
-    float m = -INFINITY;
-    for (int e = lane; e < n_out; e += 32) m = fmaxf(m, z[e]);
-    m = warp_max(m);
-    float sum = 0.0f;
-    for (int e = lane; e < n_out; e += 32) { const float p = expf(z[e] - m); score[e] = p; sum += p; }
-    sum = warp_sum(sum);
-    for (int e = lane; e < n_out; e += 32) {
-        score[e] = score[e] / sum;
-        choice[e] = score[e] + (correction ? correction[e] : 0.0f);
+    if (rule.score_fn == 0) {
+        float m = -INFINITY;
+        for (int e = lane; e < n_out; e += 32) m = fmaxf(m, z[e]);
+        m = warp_max(m);
+        float sum = 0.0f;
+        for (int e = lane; e < n_out; e += 32) { const float p = expf(z[e] - m); score[e] = p; sum += p; }
+        sum = warp_sum(sum);
+        for (int e = lane; e < n_out; e += 32) score[e] = score[e] / sum;
+    } else {
+        for (int e = lane; e < n_out; e += 32) score[e] = 1.0f / (1.0f + expf(-z[e]));
     }
+    for (int e = lane; e < n_out; e += 32) choice[e] = score[e] + (correction ? correction[e] : 0.0f);
     __syncwarp();
+    if (rule.n_groups > 1 && rule.keep_groups < rule.n_groups) {
+        const int per = n_out / rule.n_groups;
+        for (int g = lane; g < rule.n_groups; g += 32) {
+            float best[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            for (int e = g * per; e < (g + 1) * per; ++e) {
+                float v = choice[e];
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    if (v > best[k]) { const float tmp = best[k]; best[k] = v; v = tmp; }
+            }
+            float sum = 0.0f;
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (k < rule.group_top && k < per) sum += best[k];
+            gscore[g] = sum;
+        }
+        __syncwarp();
+        // the groups that stay: keep_groups times the best of those left (the lower index among equals); a group that
+        // stays gets +inf, and what is not +inf afterwards is shut out
+        for (int k = 0; k < rule.keep_groups; ++k) {
+            float best = -INFINITY;
+            int at = 0x7fffffff;
+            for (int g = lane; g < rule.n_groups; g += 32) {
+                const float v = gscore[g];
+                if (v != INFINITY && (v > best || at == 0x7fffffff)) { best = v; at = g; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+                if (oa != 0x7fffffff && (at == 0x7fffffff || ob > best || (ob == best && oa < at))) { best = ob; at = oa; }
+            }
+            if (lane == 0 && at != 0x7fffffff) gscore[at] = INFINITY;
+            __syncwarp();
+        }
+        for (int e = lane; e < n_out; e += 32)
+            if (gscore[e / per] != INFINITY) choice[e] = -INFINITY;
+        __syncwarp();
+    }
     for (int k = 0; k < top; ++k) {
         float best = -INFINITY;
         int at = 0x7fffffff;
@@ -119,14 +173,25 @@ moe_router_select_kernel(const float* __restrict__ logits, const float* __restri
         }
         __syncwarp();
     }
+    if (lane == 0 && (rule.normalize || rule.scale != 1.0f)) {
+        float sum = 0.0f;
+        for (int k = 0; k < top; ++k) sum += wts[(size_t)t * top + k];
+        const float f = rule.normalize ? rule.scale / (sum + rule.sum_eps) : rule.scale;
+        for (int k = 0; k < top; ++k) wts[(size_t)t * top + k] *= f;
+    }
 }
 
 // logits: float scratch [n_tokens, n_out].
-VCB_EXPORT int vcb_moe_router(const void* h, long long ldh, const float* wr, const float* correction, float* logits, int* ids,
-                              float* wts, int n_tokens, int width, int n_out, int top, int dtype, void* stream) {
+VCB_EXPORT int vcb_moe_router_ruled(const void* h, long long ldh, const float* wr, const float* correction, float* logits, int* ids,
+                                    float* wts, int n_tokens, int width, int n_out, int top, int score_fn, int n_groups,
+                                    int keep_groups, int group_top, int normalize, float sum_eps, float scale, int dtype,
+                                    void* stream) {
     if (n_tokens <= 0) return 0;
     if (!h || !wr || !logits || !ids || !wts || width <= 0 || n_out <= 0 || top <= 0 || top > n_out) return VCB_ERR_BAD_ARG;
-    const size_t smem = (size_t)4 * 2 * n_out * sizeof(float);
+    if (n_groups <= 0 || n_out % n_groups || keep_groups <= 0 || keep_groups > n_groups || group_top <= 0 || group_top > 4 ||
+        (score_fn != 0 && score_fn != 1) || top > (n_out / n_groups) * keep_groups)
+        return VCB_ERR_BAD_ARG;
+    const size_t smem = (size_t)4 * (2 * n_out + n_groups) * sizeof(float);
     if (smem > 48 * 1024 || (n_out + 7) / 8 > 65535) return VCB_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid((n_tokens + RT_TOK - 1) / RT_TOK, (n_out + 7) / 8);
@@ -134,8 +199,16 @@ VCB_EXPORT int vcb_moe_router(const void* h, long long ldh, const float* wr, con
     else if (dtype == VCB_BF16)
         vcb_launch(moe_router_logits_kernel<__nv_bfloat16>, grid, 256, 0, s, (const __nv_bfloat16*)h, ldh, wr, logits, n_tokens, width, n_out);
     else return VCB_ERR_BAD_ARG;
-    vcb_launch(moe_router_select_kernel, (n_tokens + 3) / 4, 128, smem, s, (const float*)logits, correction, ids, wts, n_tokens, n_out, top);
+    RouteRule rule{score_fn, n_groups, keep_groups, group_top, normalize, sum_eps, scale};
+    vcb_launch(moe_router_select_kernel, (n_tokens + 3) / 4, 128, smem, s, (const float*)logits, correction, ids, wts, n_tokens, n_out, top, rule);
     return vcb_last_error();
+}
+
+// Softmax scores, no groups, the plain scores as weights.
+VCB_EXPORT int vcb_moe_router(const void* h, long long ldh, const float* wr, const float* correction, float* logits, int* ids,
+                              float* wts, int n_tokens, int width, int n_out, int top, int dtype, void* stream) {
+    return vcb_moe_router_ruled(h, ldh, wr, correction, logits, ids, wts, n_tokens, width, n_out, top, 0, 1, 1, 1, 0, 0.0f, 1.0f,
+                                dtype, stream);
 }
 
 // --------------------------------------------------------------------------------------------- sort
@@ -204,7 +277,7 @@ __global__ void __launch_bounds__(256)
 moe_expert_gemm_kernel(const T* __restrict__ A, long long lda, const T* __restrict__ W, void* __restrict__ Cv, long long ldc,
                        int N, int K, const int* __restrict__ sorted_token, const int* __restrict__ tile_expert,
                        const int* __restrict__ tile_row0, const int* __restrict__ tile_rows, const int* __restrict__ meta,
-                       float limit, float alpha) {
+                       float limit, float alpha, float up_shift) {
     constexpr int RM = TM / 16;          // rows per thread
     __shared__ float As[MG_K][TM + 1];
     __shared__ float Ws[MG_K][MG_N + 1];
@@ -268,7 +341,7 @@ moe_expert_gemm_kernel(const T* __restrict__ A, long long lda, const T* __restri
             if (GATED) {
                 const float g = fminf(acc[i][j], limit);
                 const float u = fminf(fmaxf(accu[i][j], -limit), limit);
-                const float y = g * (1.0f / (1.0f + expf(-alpha * g))) * (u + 1.0f);
+                const float y = g * (1.0f / (1.0f + expf(-alpha * g))) * (u + up_shift);
                 ((T*)Cv)[(size_t)(r0 + m) * ldc + n] = from_f32<T>(y);
             } else {
                 ((float*)Cv)[(size_t)(r0 + m) * ldc + n] = acc[i][j];
@@ -307,7 +380,7 @@ __global__ void __launch_bounds__(128)
 moe_expert_mma_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const __nv_bfloat16* __restrict__ W, void* __restrict__ Cv,
                       long long ldc, int N, int K, const int* __restrict__ sorted_token, const int* __restrict__ tile_expert,
                       const int* __restrict__ tile_row0, const int* __restrict__ tile_rows, const int* __restrict__ meta,
-                      float limit, float alpha) {
+                      float limit, float alpha, float up_shift) {
     constexpr int WR = GATED ? 2 * MM_BN : MM_BN, MF = TM / 16;
     __shared__ __align__(16) __nv_bfloat16 As[MM_STAGES][TM][MM_LDS];
     __shared__ __align__(16) __nv_bfloat16 Ws[MM_STAGES][WR][MM_LDS];
@@ -389,7 +462,7 @@ moe_expert_mma_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const 
                 if (GATED) {
                     const float g = fminf(acc[mi][nf][c], limit);
                     const float u = fminf(fmaxf(accu[mi][nf][c], -limit), limit);
-                    const float y = g * (1.0f / (1.0f + expf(-alpha * g))) * (u + 1.0f);
+                    const float y = g * (1.0f / (1.0f + expf(-alpha * g))) * (u + up_shift);
                     ((__nv_bfloat16*)Cv)[(size_t)(r0 + m) * ldc + n] = __float2bfloat16_rn(y);
                 } else {
                     ((float*)Cv)[(size_t)(r0 + m) * ldc + n] = acc[mi][nf][c];
@@ -401,8 +474,8 @@ moe_expert_mma_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const 
 // C [pairs, N] float.  max_tiles: the grid's height; tm: 16 or 64, the tile height moe_sort was given.
 VCB_EXPORT int vcb_moe_expert_gemm(const void* A, long long lda, const void* W, void* C, long long ldc, int N, int K,
                                    const int* sorted_token, const int* tile_expert, const int* tile_row0, const int* tile_rows,
-                                   const int* meta, int max_tiles, int tm, int gated, float limit, float alpha, int dtype,
-                                   void* stream) {
+                                   const int* meta, int max_tiles, int tm, int gated, float limit, float alpha, float up_shift,
+                                   int dtype, void* stream) {
     if (max_tiles <= 0) return 0;
     if (!A || !W || !C || N <= 0 || K <= 0 || (tm != 16 && tm != 64) || max_tiles > 65535) return VCB_ERR_BAD_ARG;
     dim3 grid((N + MG_N - 1) / MG_N, max_tiles);
@@ -410,14 +483,14 @@ VCB_EXPORT int vcb_moe_expert_gemm(const void* A, long long lda, const void* W, 
     if (dtype == VCB_BF16 && K % 8 == 0 && lda % 8 == 0 && !(((uintptr_t)A | (uintptr_t)W) & 15)) {
         // the tensor-core form
 #define MOE_MMA(TMV, G) vcb_launch(moe_expert_mma_kernel<TMV, G>, grid, 128, 0, s, (const __nv_bfloat16*)A, lda, (const __nv_bfloat16*)W, C, ldc, N, K, \
-                                   sorted_token, tile_expert, tile_row0, tile_rows, meta, limit, alpha)
+                                   sorted_token, tile_expert, tile_row0, tile_rows, meta, limit, alpha, up_shift)
         if (tm == 16) { if (gated) MOE_MMA(16, true); else MOE_MMA(16, false); }
         else { if (gated) MOE_MMA(64, true); else MOE_MMA(64, false); }
 #undef MOE_MMA
         return vcb_last_error();
     }
 #define MOE_GO(TT, TMV, G) vcb_launch(moe_expert_gemm_kernel<TT, TMV, G>, grid, 256, 0, s, (const TT*)A, lda, (const TT*)W, C, ldc, N, K, \
-                                      sorted_token, tile_expert, tile_row0, tile_rows, meta, limit, alpha)
+                                      sorted_token, tile_expert, tile_row0, tile_rows, meta, limit, alpha, up_shift)
     if (dtype == VCB_F32) {
         if (tm == 16) { if (gated) MOE_GO(float, 16, true); else MOE_GO(float, 16, false); }
         else { if (gated) MOE_GO(float, 64, true); else MOE_GO(float, 64, false); }

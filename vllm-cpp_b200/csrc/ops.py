@@ -63,10 +63,18 @@ _SIGNATURES = {
     "vcb_gated_group_norm": [_P, _L, _P, _L, _P, _I, _P, _L, _I, _I, _I, _I, _F, _I, _P],
     "vcb_scaled_sum": [_P, _P, _P, _L, _F, _F, _I, _P],
     "vcb_qk_norm_cache_write": [_P, _L, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _I, _P],
-    "vcb_attention_biased": [_P, _P, _P, _P, _L, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _I, _P],
+    "vcb_attention_biased": [_P, _P, _P, _P, _L, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P, _I, _I, _P],
+    "vcb_qk_head_rope_cache_write": [_P, _L, _I, _I, _I, _P, _P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _I, _P],
     "vcb_moe_router": [_P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "vcb_moe_router_ruled": [_P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P],
+    "vcb_stream_norm": [_P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _F, _F, _I, _P],
+    "vcb_stream_join": [_P, _L, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _I, _P],
+    "vcb_causal_conv": [_P, _L, _P, _P, _P, _P, _L, _P, _L, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "vcb_gate_blocks": [_P, _L, _P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _F, _I, _P],
+    "vcb_linear_recurrence": [_P, _P, _L, _P, _L, _P, _P, _L, _P, _L, _P, _P, _I, _I, _I, _P],
+    "vcb_gated_delta_scan": [_P, _P, _P, _L, _L, _L, _P, _L, _P, _L, _P, _P, _P, _P, _L, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _P],
     "vcb_moe_sort": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P],
-    "vcb_moe_expert_gemm": [_P, _L, _P, _P, _L, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _F, _F, _I, _P],
+    "vcb_moe_expert_gemm": [_P, _L, _P, _P, _L, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _F, _F, _F, _I, _P],
     "vcb_moe_combine": [_P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _P],
 }
 
@@ -1013,17 +1021,21 @@ def qk_norm_cache_write(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, 
 
 def attention_biased(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor], positions,
                      req_of_token, block_table, bias: Optional[torch.Tensor], *, num_heads: int, num_kv_heads: int,
-                     head_dim: int, v_head_dim: int, row: int, page_size: int, window: int, scale: float, cap: float) -> None:
+                     head_dim: int, v_head_dim: int, row: int, page_size: int, window: int, scale: float, cap: float,
+                     sink: Optional[torch.Tensor] = None, gate_per_head: bool = False) -> None:
     """Paged attention with  score = cap * tanh(scale * q.k / cap) + bias[min(distance, len(bias) - 1), head]  (cap <= 0: no
     cap; bias float32 [distances, heads] or None), softmax over the keys the window leaves, values of ``v_head_dim``,
-    and out *= sigmoid(gate) when a gate ([n, heads * v_head_dim] rows) is given."""
+    and out *= sigmoid(gate) when a gate is given ([n, heads * v_head_dim] rows, or with ``gate_per_head`` [n, heads]: one
+    number per head).  ``sink`` (float32 [heads]): a logit per head that joins the softmax's denominator once, unscaled,
+    and has no value."""
     n = q.shape[0]
     _need(q.shape == (n, num_heads * head_dim) and out.shape == (n, num_heads * v_head_dim) and out.dtype == q.dtype
           and cache.dtype == q.dtype, "attention_biased: shapes or types")
     _need(v_head_dim <= 256 and head_dim <= 1024, "attention_biased: head sizes up to 1024 (keys) and 256 (values)")
     if gate is not None:
         _rows(gate, "gate", q.dtype)
-        _need(gate.shape == out.shape, "attention_biased: gate like out")
+        _need(gate.shape == ((n, num_heads) if gate_per_head else out.shape), "attention_biased: gate like out, or one column per head")
+    _need(sink is None or sink.numel() == num_heads, "attention_biased: one sink per head")
     if bias is not None:
         _need(bias.dim() == 2 and bias.shape[1] == num_heads, "attention_biased: bias [distances, heads]")
     _check(lib().vcb_attention_biased(
@@ -1032,7 +1044,33 @@ def attention_biased(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, ga
         _dev(req_of_token, "req_of_token", torch.int32), _dev(block_table, "block_table", torch.int32), block_table.shape[1],
         None if bias is None else _dev(bias, "bias", torch.float32), 0 if bias is None else bias.shape[0], n, num_heads,
         num_kv_heads, head_dim, v_head_dim, row, page_size, window, float(scale), float(cap), cache.shape[0],
-        status_tensor(q.device).data_ptr(), dtype_code(q.dtype), _stream()), "attention_biased")
+        status_tensor(q.device).data_ptr(), None if sink is None else _dev(sink, "sink", torch.float32),
+        1 if gate_per_head else 0, dtype_code(q.dtype), _stream()), "attention_biased")
+
+
+def qk_head_rope_cache_write(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, wq: Optional[torch.Tensor],
+                             wk: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor], q_out: torch.Tensor,
+                             cache: torch.Tensor, positions, req_of_token, block_table, *, num_heads: int, num_kv_heads: int,
+                             head_dim: int, v_head_dim: int, row: int, page_size: int, eps: float, write_kv: bool) -> None:
+    """As qk_norm_cache_write, but queries and keys are RMS-normed head by head over ``head_dim`` with gains ``wq`` / ``wk``
+    (float32 [head_dim], shared by the heads; None: not normed) and then rotated on their first 2 * len(inv_freq)
+    coordinates (coordinate i pairs with i + len(inv_freq); angle = position * inv_freq[i], float32)."""
+    n = proj.shape[0]
+    _rows(proj, "proj", proj.dtype)
+    _need(q_out.shape == (n, num_heads * head_dim) and q_out.dtype == proj.dtype and cache.dtype == proj.dtype, "qk_head_rope_cache_write: types")
+    _need(wq is None or wq.numel() == head_dim, "qk_head_rope_cache_write: one query gain per coordinate of a head")
+    _need(wk is None or wk.numel() == head_dim, "qk_head_rope_cache_write: one key gain per coordinate of a head")
+    rot = 0 if inv_freq is None else 2 * inv_freq.numel()
+    _need(rot <= head_dim, "qk_head_rope_cache_write: more rotated coordinates than a head has")
+    _need(cache.is_contiguous() and cache.numel() == cache.shape[0] * 2 * num_kv_heads * page_size * row,
+          "qk_head_rope_cache_write: a cache of key and value planes with rows of `row` elements")
+    _check(lib().vcb_qk_head_rope_cache_write(
+        proj.data_ptr(), proj.stride(0), q_off, k_off, v_off, None if wq is None else _dev(wq, "wq", torch.float32),
+        None if wk is None else _dev(wk, "wk", torch.float32), None if inv_freq is None else _dev(inv_freq, "inv_freq", torch.float32),
+        rot, _dev(q_out, "q_out"), cache.data_ptr(), _dev(positions, "positions", torch.int32),
+        _dev(req_of_token, "req_of_token", torch.int32), _dev(block_table, "block_table", torch.int32), block_table.shape[1], n,
+        num_heads, num_kv_heads, head_dim, v_head_dim, row, page_size, cache.shape[0], 1 if write_kv else 0, float(eps),
+        status_tensor(proj.device).data_ptr(), dtype_code(proj.dtype), _stream()), "qk_head_rope_cache_write")
 
 
 # ------------------------------------------------- routed experts
@@ -1050,21 +1088,34 @@ def moe_max_tiles(n_tokens: int, top: int, n_experts: int, tm: int) -> int:
     return min(pairs, pairs // tm + n_experts)
 
 
+ROUTER_SCORES = {"softmax": 0, "sigmoid": 1}
+ROUTER_GROUP_TOP_MAX = 4
+
+
 def moe_router(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], ids: torch.Tensor,
-               weights: torch.Tensor, logits: torch.Tensor) -> None:
-    """For every row of h: scores = softmax(w_router h) in float32 over all router outputs; ids [n, top] = the outputs
-    with the largest score + correction (the lower index wins among equals), weights [n, top] = their plain scores.
-    ``logits``: float32 scratch [n, router outputs].  Two kernels (csrc/moe.cu)."""
+               weights: torch.Tensor, logits: torch.Tensor, *, score: str = "softmax", groups: int = 1, keep_groups: int = 1,
+               group_top: int = 1, normalize: bool = False, sum_eps: float = 0.0, scale: float = 1.0) -> None:
+    """For every row of h: scores in float32 from the logits w_router h, by softmax over all router outputs or by a
+    sigmoid of each (``score``); ids [n, top] = the outputs with the largest score + correction (the lower index wins
+    among equals), with ``groups`` > ``keep_groups`` only among the ``keep_groups`` best of ``groups`` equal groups of
+    neighbouring outputs (a group's score: the sum of its ``group_top`` largest); weights [n, top] = their plain scores,
+    with ``normalize`` divided by (their sum + ``sum_eps``), times ``scale``.  ``logits``: float32 scratch
+    [n, router outputs].  Two kernels (csrc/moe.cu)."""
+    _need(score in ROUTER_SCORES, f"moe_router: score is one of {sorted(ROUTER_SCORES)}")
+    _need(groups >= 1 and w_router.shape[0] % groups == 0 and 1 <= keep_groups <= groups and 1 <= group_top <= ROUTER_GROUP_TOP_MAX,
+          "moe_router: equal groups, some of them kept, a group's score from at most four outputs")
+    _need(ids.shape[1] <= w_router.shape[0] // groups * keep_groups, "moe_router: more choices than the kept groups hold")
     n, width = h.shape
     _rows(h, "h", h.dtype)
     top = ids.shape[1]
     _need(w_router.shape[1] == width and ids.shape == (n, top) and weights.shape == (n, top), "moe_router: shapes")
     _need(correction is None or correction.numel() == w_router.shape[0], "moe_router: one correction per router output")
     _need(logits.dtype == torch.float32 and logits.is_contiguous() and logits.numel() >= n * w_router.shape[0], "moe_router: logits scratch")
-    _check(lib().vcb_moe_router(h.data_ptr(), h.stride(0), _dev(w_router, "w_router", torch.float32),
-                                None if correction is None else _dev(correction, "correction", torch.float32),
-                                logits.data_ptr(), _dev(ids, "ids", torch.int32), _dev(weights, "weights", torch.float32), n, width,
-                                w_router.shape[0], top, dtype_code(h.dtype), _stream()), "moe_router")
+    _check(lib().vcb_moe_router_ruled(h.data_ptr(), h.stride(0), _dev(w_router, "w_router", torch.float32),
+                                      None if correction is None else _dev(correction, "correction", torch.float32),
+                                      logits.data_ptr(), _dev(ids, "ids", torch.int32), _dev(weights, "weights", torch.float32), n, width,
+                                      w_router.shape[0], top, ROUTER_SCORES[score], groups, keep_groups, group_top,
+                                      1 if normalize else 0, float(sum_eps), float(scale), dtype_code(h.dtype), _stream()), "moe_router")
     add_launches(1)                # logits and selection
 
 
@@ -1082,10 +1133,11 @@ def moe_sort(ids: torch.Tensor, n_experts: int, tm: int, sorted_token, pos, tile
 
 
 def moe_expert_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, sorted_token, tile_expert, tile_row0, tile_rows, meta,
-                    max_tiles: int, tm: int, *, gated: bool, limit: float = 0.0, alpha: float = 0.0) -> None:
+                    max_tiles: int, tm: int, *, gated: bool, limit: float = 0.0, alpha: float = 0.0, up_shift: float = 1.0) -> None:
     """The experts' products over the tiles of moe_sort.  gated: a [n, K] the tokens' rows, w [E, 2 * N, K] gate rows then
-    up rows, out [pairs, N] of the activations' type = g * sigmoid(alpha * g) * (u + 1) with g = min(gate, limit),
-    u = clamp(up, -limit, limit).  Not gated: a [pairs, K] the sorted rows, w [E, N, K], out [pairs, N] float32."""
+    up rows, out [pairs, N] of the activations' type = g * sigmoid(alpha * g) * (u + up_shift) with g = min(gate, limit),
+    u = clamp(up, -limit, limit) (limit inf, alpha 1, up_shift 0: silu(gate) * up).  Not gated: a [pairs, K] the sorted
+    rows, w [E, N, K], out [pairs, N] float32."""
     _rows(a, "a", a.dtype)
     _need(w.dim() == 3 and w.is_contiguous() and w.dtype == a.dtype and w.shape[2] == a.shape[1], "moe_expert_gemm: w [E, N, K]")
     N = w.shape[1] // 2 if gated else w.shape[1]
@@ -1093,7 +1145,7 @@ def moe_expert_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, sorted_
     _need(out.shape[1] == N and tm in MOE_TILE_ROWS, "moe_expert_gemm: out [pairs, N]")
     _check(lib().vcb_moe_expert_gemm(a.data_ptr(), a.stride(0), w.data_ptr(), out.data_ptr(), out.stride(0), N, a.shape[1],
                                      sorted_token.data_ptr(), tile_expert.data_ptr(), tile_row0.data_ptr(), tile_rows.data_ptr(),
-                                     meta.data_ptr(), max_tiles, tm, 1 if gated else 0, float(limit), float(alpha),
+                                     meta.data_ptr(), max_tiles, tm, 1 if gated else 0, float(limit), float(alpha), float(up_shift),
                                      dtype_code(a.dtype), _stream()), "moe_expert_gemm")
 
 
@@ -1105,6 +1157,144 @@ def moe_combine(y: torch.Tensor, h: torch.Tensor, pos: torch.Tensor, weights: to
     _check(lib().vcb_moe_combine(y.data_ptr(), h.data_ptr(), h.stride(0), _dev(pos, "pos", torch.int32),
                                  _dev(weights, "weights", torch.float32), _dev(out, "out"), n, width, weights.shape[1],
                                  dtype_code(out.dtype), _stream()), "moe_combine")
+
+
+# ------------------------------------------------- a residual stream of several copies, read through a layer norm
+STREAMS_MAX = 8
+
+
+def _streams(x: torch.Tensor, name: str):
+    _need(x.dim() == 3 and x.dtype == torch.float32 and x.is_cuda and x.stride(2) == 1 and x.stride(1) == x.shape[2]
+          and 1 <= x.shape[0] <= STREAMS_MAX, f"{name}: float32 streams [S <= {STREAMS_MAX}, n, hidden] with contiguous rows")
+    return x.shape
+
+
+def stream_norm(x: torch.Tensor, coef: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], out: torch.Tensor, eps: float,
+                row_index: Optional[torch.Tensor] = None, out_scale: float = 1.0) -> None:
+    """out = layer_norm(sum_s coef[s] x[s]) * w + b, times ``out_scale``; mean and variance (the mean of the squared
+    deviations) in float32.  x float32 [S, n, hidden]; with ``row_index`` out row o reads row row_index[o]."""
+    S, n, hidden = _streams(x, "stream_norm")
+    rows = out.shape[0]
+    _need(out.shape[1] == hidden and w.numel() == hidden and (b is None or b.numel() == hidden) and coef.numel() == S, "stream_norm: widths")
+    _need(rows == n if row_index is None else row_index.numel() == rows, "stream_norm: one output row per row read")
+    _check(lib().vcb_stream_norm(x.data_ptr(), x.stride(0), _dev(coef, "coef", torch.float32), _dev(w, "w", torch.float32),
+                                 None if b is None else _dev(b, "b", torch.float32), _dev(out, "out"),
+                                 None if row_index is None else _dev(row_index, "row_index", torch.int32), rows, S, hidden,
+                                 float(eps), float(out_scale), dtype_code(out.dtype), _stream()), "stream_norm")
+
+
+def stream_join(x: torch.Tensor, y: torch.Tensor, mix: torch.Tensor, out_coef: torch.Tensor, eps: float = 0.0,
+                next_coef: Optional[torch.Tensor] = None, next_w: Optional[torch.Tensor] = None,
+                next_b: Optional[torch.Tensor] = None, next_out: Optional[torch.Tensor] = None) -> None:
+    """x[t] <- sum_s mix[s, t] x[s] + out_coef[t] y for all streams at once, in float32 in place; with ``next_out``:
+    next_out = layer_norm(sum_t next_coef[t] x[t]) * next_w + next_b, the input of the sublayer that follows."""
+    S, n, hidden = _streams(x, "stream_join")
+    _need(y.shape == (n, hidden) and mix.numel() == S * S and out_coef.numel() == S, "stream_join: shapes")
+    if next_out is not None:
+        _need(next_coef is not None and next_coef.numel() == S and next_w is not None and next_w.numel() == hidden
+              and (next_b is None or next_b.numel() == hidden) and next_out.shape == (n, hidden) and next_out.dtype == y.dtype,
+              "stream_join: the next sublayer's coefficients, norm and input")
+    _check(lib().vcb_stream_join(x.data_ptr(), x.stride(0), _dev(y, "y"), _dev(mix, "mix", torch.float32),
+                                 _dev(out_coef, "out_coef", torch.float32),
+                                 None if next_out is None else _dev(next_coef, "next_coef", torch.float32),
+                                 None if next_out is None else _dev(next_w, "next_w", torch.float32),
+                                 None if next_out is None or next_b is None else _dev(next_b, "next_b", torch.float32),
+                                 None if next_out is None else _dev(next_out, "next_out"), n, S, hidden, float(eps),
+                                 dtype_code(y.dtype), _stream()), "stream_join")
+
+
+# ------------------------------------------------- recurrent mixers behind a short convolution
+CONV_MAX_TAPS = 8
+
+
+def causal_conv(x: torch.Tensor, taps: torch.Tensor, state: torch.Tensor, out: torch.Tensor, q_start, state_slots, n_reqs: int,
+                max_q_len: int, *, pre_bias: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+                act: str = "none") -> None:
+    """out[t, c] = act(sum_j taps[c, j] * in[t - (J - 1) + j, c] + bias[c]) over each request's tokens, in = x + pre_bias;
+    the J - 1 inputs before a request's first token of the step come from its slot of ``state`` (float32
+    [slots, >= J - 1 rows, C] as a strided view: rows 0 .. J - 2, oldest first; zero at admission), which then receives the
+    step's last J - 1 inputs.  x rows of the activations' type [n, C]; taps float32 [C, J]; out float32 [n, C] rows."""
+    n, C = x.shape
+    J = taps.shape[1]
+    _rows(x, "x", x.dtype)
+    _rows(out, "out", torch.float32)
+    _need(out.shape == (n, C) and taps.shape[0] == C and 1 <= J <= CONV_MAX_TAPS, f"causal_conv: taps [C, up to {CONV_MAX_TAPS}]")
+    _need(act in ("none", "silu"), "causal_conv: act is 'none' or 'silu'")
+    _need(state.dtype == torch.float32 and state.dim() == 3 and state.shape[2] == C and state.shape[1] >= J - 1
+          and state.stride(2) == 1 and (J == 1 or state.shape[1] == 1 or state.stride(1) == C),
+          "causal_conv: state float32 [slots, J - 1, C] with contiguous rows")
+    for t, name in ((pre_bias, "pre_bias"), (bias, "bias")):
+        _need(t is None or t.numel() == C, f"causal_conv: {name} [C]")
+    _check(lib().vcb_causal_conv(x.data_ptr(), x.stride(0), None if pre_bias is None else _dev(pre_bias, "pre_bias", torch.float32),
+                                 _dev(taps, "taps", torch.float32), None if bias is None else _dev(bias, "bias", torch.float32),
+                                 state.data_ptr(), state.stride(0), out.data_ptr(), out.stride(0),
+                                 _dev(q_start, "q_start", torch.int32), _dev(state_slots, "state_slots", torch.int32), n_reqs,
+                                 max_q_len, C, J, 1 if act == "silu" else 0, dtype_code(x.dtype), _stream()), "causal_conv")
+
+
+def gate_blocks(u: torch.Tensor, wa: torch.Tensor, wi: torch.Tensor, ba: torch.Tensor, bi: torch.Tensor, lam: torch.Tensor,
+                decay: torch.Tensor, drive: torch.Tensor, c_gate: float) -> None:
+    """Per block b of W / B channels:  r = sigmoid(wa[b] u_b + ba), i = sigmoid(wi[b] u_b + bi);
+    decay = exp(-c_gate * r * softplus(lam)), drive = sqrt(1 - decay^2) * i * u.  u, decay, drive float32 [n, W]; wa, wi
+    [B, W / B, W / B] ([out, in]) of the weights' type; the sums, gates and exponentials float32."""
+    n, W = u.shape
+    B = wa.shape[0]
+    _rows(u, "u", torch.float32)
+    _need(wa.dim() == 3 and wa.shape == wi.shape and wa.shape[1] == wa.shape[2] and B * wa.shape[1] == W and wa.dtype == wi.dtype,
+          "gate_blocks: square blocks that fill the width")
+    _need(decay.shape == u.shape and drive.shape == u.shape and decay.is_contiguous() and drive.is_contiguous()
+          and decay.dtype == drive.dtype == torch.float32, "gate_blocks: outputs like u")
+    _check(lib().vcb_gate_blocks(u.data_ptr(), u.stride(0), _dev(wa, "wa"), _dev(wi, "wi"), _dev(ba, "ba", torch.float32),
+                                 _dev(bi, "bi", torch.float32), _dev(lam, "lam", torch.float32), decay.data_ptr(), drive.data_ptr(),
+                                 decay.stride(0), n, W, B, float(c_gate), dtype_code(wa.dtype), _stream()), "gate_blocks")
+
+
+def linear_recurrence(decay: torch.Tensor, drive: torch.Tensor, y: torch.Tensor, y_bias: Optional[torch.Tensor],
+                      state: torch.Tensor, out: torch.Tensor, q_start, state_slots, n_reqs: int) -> None:
+    """S_t = decay_t * S_(t-1) + drive_t per channel and request, S read from and left in the request's slot of ``state``
+    (float32 [slots, W] as a strided view); out = S_t * gelu_tanh(y_t + y_bias) in the activations' type."""
+    n, W = decay.shape
+    _need(decay.is_contiguous() and drive.is_contiguous() and drive.shape == decay.shape and decay.dtype == drive.dtype == torch.float32,
+          "linear_recurrence: decay and drive float32 [n, W]")
+    _rows(y, "y", out.dtype)
+    _rows(out, "out", out.dtype)
+    _need(y.shape == (n, W) and out.shape == (n, W) and (y_bias is None or y_bias.numel() == W), "linear_recurrence: shapes")
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.shape[1] == W and state.stride(1) == 1, "linear_recurrence: state [slots, W]")
+    _check(lib().vcb_linear_recurrence(decay.data_ptr(), drive.data_ptr(), decay.stride(0), y.data_ptr(), y.stride(0),
+                                       None if y_bias is None else _dev(y_bias, "y_bias", torch.float32), state.data_ptr(),
+                                       state.stride(0), out.data_ptr(), out.stride(0), _dev(q_start, "q_start", torch.int32),
+                                       _dev(state_slots, "state_slots", torch.int32), n_reqs, W, dtype_code(out.dtype), _stream()),
+           "linear_recurrence")
+
+
+def gated_delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta_pre: torch.Tensor, decay_pre: torch.Tensor,
+                     a_log: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor, out: torch.Tensor, q_start, state_slots,
+                     n_reqs: int, *, num_heads: int, num_qk_heads: int, q_scale: float, unit_eps: float) -> None:
+    """The gated delta rule per request and head over the step's tokens, S (float32 [dk, dv]) read from and left in the
+    request's slot of ``state`` [slots, heads, dk, dv]:
+        S <- diag(g_t) S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  out_t = S^T q_t
+    q, k float32 rows [n, qk heads * dk] (made unit vectors per head here: x / sqrt(sum x^2 + unit_eps); q times
+    ``q_scale``), head h reading qk head h // (heads / qk heads); v float32 rows [n, heads * dv]; beta = sigmoid(beta_pre
+    [n, heads]); g = exp(-exp(a_log[h]) * softplus(decay_pre [n, heads * dk] + dt_bias)); out float32 [n, heads * dv]."""
+    n = q.shape[0]
+    H, G = num_heads, num_qk_heads
+    _need(H % G == 0 and q.shape[1] % G == 0 and v.shape[1] % H == 0, "gated_delta_scan: head counts")
+    dk, dv = q.shape[1] // G, v.shape[1] // H
+    for t, name in ((q, "q"), (k, "k"), (v, "v"), (out, "out")):
+        _rows(t, name, torch.float32)
+    _rows(beta_pre, "beta_pre", beta_pre.dtype)
+    _rows(decay_pre, "decay_pre", beta_pre.dtype)
+    _need(k.shape == q.shape and v.shape[0] == n and out.shape == (n, H * dv) and beta_pre.shape == (n, H)
+          and decay_pre.shape == (n, H * dk), "gated_delta_scan: shapes")
+    _need(dk <= 1024, "gated_delta_scan: key heads of up to 1024 channels")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (H, dk, dv),
+          "gated_delta_scan: state float32 [slots, heads, dk, dv]")
+    _check(lib().vcb_gated_delta_scan(q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), k.stride(0), v.stride(0),
+                                      beta_pre.data_ptr(), beta_pre.stride(0), decay_pre.data_ptr(), decay_pre.stride(0),
+                                      _dev(a_log, "a_log", torch.float32), _dev(dt_bias, "dt_bias", torch.float32),
+                                      state.data_ptr(), out.data_ptr(), out.stride(0), _dev(q_start, "q_start", torch.int32),
+                                      _dev(state_slots, "state_slots", torch.int32), n_reqs, H, G, dk, dv, float(q_scale),
+                                      float(unit_eps), dtype_code(beta_pre.dtype), _stream()), "gated_delta_scan")
 
 
 # ------------------------------------------------------------------ latent attention

@@ -27,6 +27,7 @@ class ParamSpec:
     role "bias":   added in float, held in float32, random N(0, std).
     role "gain":   a norm's scale, held in float32, random 1 + N(0, gain_std).
     role "offset_gain": a norm's scale stored around zero (the part adds 1), held in float32, random N(0, gain_std).
+    role "identity": a small square matrix of coefficients, held in float32, random identity + N(0, gain_std).
 
     A dimension of -1 is free: the checkpoint's tensor gives it (a table whose length no configuration key
     names); ``default_shape`` is then what the random-weights mode makes.

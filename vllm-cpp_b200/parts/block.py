@@ -179,3 +179,65 @@ class SandwichNormBlock(Block):
         ops.norm_residual_norm(y, last[0], residual, last[1], next_gain=after[0], next_out=delta, next_eps=after[1])
         ws.release(mark)
         return NormedInput()
+
+
+@register_block("hyper_prenorm")
+class HyperConnectionBlock(Block):
+    """Pre-norm sublayers on a residual stream kept as several copies x_1 .. x_s (hyper-connections):
+
+        u = sum_s read_1[s] x_s;  y = mixer(mixer_norm(u));         x_t <- sum_s mix_1[s, t] x_s + write_1[t] y
+        u = sum_s read_2[s] x_s;  y = feed_forward(feed_forward_norm(u));  x_t <- sum_s mix_2[s, t] x_s + write_2[t] y
+
+    ``mixer_streams`` / ``feed_forward_streams`` (family "stream_mixing") hold the coefficients; with the "plain" kind
+    this is the ordinary pre-norm layer on one stream.  ``residual`` is float32 [streams, n, hidden] (the model class
+    "stream_decoder" makes it).  The join of a sublayer's result, the read of the sublayer that follows and its norm
+    are one kernel (ops.stream_join), also across layers of this arrangement (NormedInput).  A layer whose feed-forward
+    is "none" has only the first line.  The norms are any norm with ``forward_streams`` (parts/norm.py "layernorm")."""
+
+    SLOTS = {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_norm": "norm", "feed_forward_norm": "norm",
+             "mixer_streams": "stream_mixing", "feed_forward_streams": "stream_mixing"}
+
+    def __init__(self, params=None, **parts):
+        super().__init__(params=params, **parts)
+        self.has_ff = not isinstance(self.feed_forward, NoFeedForward)
+        if self.has_ff and self.mixer_streams.streams != self.feed_forward_streams.streams:
+            raise ValueError("hyper_prenorm: both sublayers must see the same number of streams")
+        self.streams = self.mixer_streams.streams
+
+    def stream_input(self):
+        """(coefficients, norm) with which this block reads the streams first."""
+        return self.mixer_streams.read, self.mixer_norm
+
+    def workspace_bytes(self, n_tokens, n_reqs, hidden, dtype):
+        return 2 * workspace_piece((n_tokens, hidden), dtype) + super().workspace_bytes(n_tokens, n_reqs, hidden, dtype)
+
+    def forward(self, residual, delta, pending, step, cache, writes_cache, ws, next_block=None, carry=None):
+        if residual.dim() != 3 or residual.shape[0] != self.streams:
+            raise ValueError(f"hyper_prenorm: the residual stream must be [{self.streams}, tokens, hidden]; the model "
+                             "class 'stream_decoder' makes it so")
+        if pending is not False and not isinstance(pending, NormedInput):
+            raise ValueError("hyper_prenorm takes the streams as they are, or its own normed input")
+        mark = ws.mark()
+        n, hidden = residual.shape[1:]
+        y = ws.take((n, hidden), delta.dtype)
+        if isinstance(pending, NormedInput):
+            h = delta
+        else:
+            h = ws.take((n, hidden), delta.dtype)
+            self.mixer_norm.forward_streams(residual, self.mixer_streams.read, h)
+        self.mixer.forward(h, y, step, cache, writes_cache, ws)
+        last = self.mixer_streams
+        if self.has_ff:
+            fs, fn = self.feed_forward_streams, self.feed_forward_norm
+            ops.stream_join(residual, y, last.mix, last.write, fn.eps, next_coef=fs.read, next_w=fn.weight, next_b=fn.bias, next_out=h)
+            self.feed_forward.forward(h, y, step, ws)
+            last = fs
+        if isinstance(next_block, HyperConnectionBlock) and next_block.streams == self.streams:
+            coef, norm = next_block.stream_input()
+            ops.stream_join(residual, y, last.mix, last.write, norm.eps, next_coef=coef, next_w=norm.weight, next_b=norm.bias,
+                            next_out=delta)
+            ws.release(mark)
+            return NormedInput()
+        ops.stream_join(residual, y, last.mix, last.write)
+        ws.release(mark)
+        return False

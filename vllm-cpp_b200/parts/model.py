@@ -23,7 +23,8 @@ from .base import BLOCKS, FAMILIES, NORMS, ParamSpec, StepContext, Workspace, bu
 # importing the modules registers the built-in parts
 from . import (attention as _attention, biased_attention as _biased, block as _block, gate as _gate,  # noqa: F401
                latent_attention as _latent, linear_attention as _linear, mlp as _mlp, moe as _moe, norm as _norm,
-               parallel as _parallel, position as _position, scale as _scale, shift as _shift)
+               gated_recurrence as _gated_recurrence, parallel as _parallel, position as _position, scale as _scale,
+               shift as _shift, sink_attention as _sink_attention, streams as _streams)
 
 TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
@@ -158,7 +159,7 @@ class DecoderModel:
                 logits: torch.Tensor) -> torch.Tensor:
         """Runs the step's tokens; fills and returns logits[:n_logit_rows] (float32 [rows, vocab])."""
         n = step.n_tokens
-        residual = ws.take((n, self.hidden), torch.float32)
+        residual = ws.take(self.residual_shape(n), torch.float32)
         delta = ws.take((n, self.hidden), self.dtype)
         carry = ws.take((2, ops.sumsq_parts(self.hidden), n), torch.float32)
         self.embed_tokens(step, residual)
@@ -174,12 +175,20 @@ class DecoderModel:
         out = logits[:m]
         if m:
             normed = ws.take((m, self.hidden), self.dtype)
-            self.final_norm.forward(residual, delta if has_delta else None, normed, step.logit_rows)
+            self.final_rows(residual, delta if has_delta else None, normed, step)
             self.head(normed, out)
         return out
 
-    # Two places an architecture may differ at without touching its layers; a subclass registered with
+    # Places an architecture may differ at without touching its layers; a subclass registered with
     # register_model_class overrides them (and ModelSpec.model_class names it).
+    def residual_shape(self, n_tokens: int):
+        """Shape of the float32 residual stream of a step (what the blocks receive as ``residual``)."""
+        return (n_tokens, self.hidden)
+
+    def final_rows(self, residual: torch.Tensor, delta: Optional[torch.Tensor], normed: torch.Tensor, step: StepContext) -> None:
+        """normed = the model's final norm of the rows whose logits are wanted (``delta``: an addition still pending)."""
+        self.final_norm.forward(residual, delta, normed, step.logit_rows)
+
     def embed_tokens(self, step: StepContext, residual: torch.Tensor) -> None:
         """residual[t] = the embedding of token t in float32 (src/kernels/embedding_kernel.cu:20-28: no scaling)."""
         ops.embedding(self.embed, step.token_ids, residual)
@@ -193,7 +202,10 @@ class DecoderModel:
         largest need of any block (each piece rounded up as Workspace.take rounds)."""
         el = torch.empty((), dtype=self.dtype).element_size()
         r = lambda b: (b + 255) // 256 * 256
-        own = r(n_tokens * self.hidden * 4) + r(n_tokens * self.hidden * el) \
+        rows = 1
+        for d in self.residual_shape(n_tokens)[:-1]:
+            rows *= d
+        own = r(rows * self.hidden * 4) + r(n_tokens * self.hidden * el) \
             + r(2 * ops.sumsq_parts(self.hidden) * n_tokens * 4) + r(n_logit_rows * self.hidden * el)
         return own + max((blk.workspace_bytes(n_tokens, n_reqs, self.hidden, self.dtype) for blk in self.blocks), default=0)
 
@@ -233,3 +245,35 @@ class ScaledSinusoidDecoderModel(DecoderModel):
 
     def embed_tokens(self, step, residual):
         ops.embedding_sinusoid(self.embed, step.token_ids, step.positions, self.inv_freq, residual, self.embedding_scale)
+
+
+@register_model_class("stream_decoder")
+class StreamDecoderModel(DecoderModel):
+    """A decoder whose residual stream is ``streams`` copies of the embedding (ModelSpec.model_params), which its
+    layers read and rejoin with coefficients of their own (parts/block.py "hyper_prenorm"); the final norm reads the
+    sum of the copies.  ``streams`` 1 is one plain residual stream."""
+
+    def __init__(self, spec, dtype, device):
+        self.streams = int(spec.model_params.get("streams", 1))
+        super().__init__(spec, dtype, device)
+        if not hasattr(self.final_norm, "forward_streams"):
+            raise ValueError("stream_decoder: the final norm must read several streams (forward_streams)")
+        for i, blk in enumerate(self.blocks):
+            if getattr(blk, "streams", None) != self.streams:
+                raise ValueError(f"stream_decoder: layer {i} does not take {self.streams} streams")
+        self._ones = None if torch.device(device).type == "meta" else torch.ones(self.streams, dtype=torch.float32, device=device)
+
+    def tensors(self):
+        return super().tensors() + ([self._ones] if self._ones is not None else [])
+
+    def residual_shape(self, n_tokens):
+        return (self.streams, n_tokens, self.hidden)
+
+    def embed_tokens(self, step, residual):
+        for s in range(self.streams):
+            ops.embedding(self.embed, step.token_ids, residual[s])
+
+    def final_rows(self, residual, delta, normed, step):
+        if delta is not None:
+            raise ValueError("stream_decoder: its layers leave no addition pending")
+        self.final_norm.forward_streams(residual, self._ones, normed, step.logit_rows)

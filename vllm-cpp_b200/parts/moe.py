@@ -1,12 +1,16 @@
 """A feed-forward of routed experts.
 
-    s = softmax(W_r h)                      float32, over ``num_experts`` + ``num_identity`` router outputs
-    chosen = the ``top`` outputs with the largest s + correction;  weights = s[chosen], as they are
+    s = softmax(W_r h)  or  sigmoid(W_r h)  float32, over ``num_experts`` + ``num_identity`` router outputs (``score``)
+    chosen = the ``top`` outputs with the largest s + correction (``correction`` False: no such tensor); with
+             ``groups`` > ``keep_groups`` only outputs of the ``keep_groups`` best of ``groups`` equal groups of neighbours
+             may be chosen, a group's score being the sum of its ``group_top`` largest
+    weights = s[chosen]; with ``normalize`` divided by (their sum + ``sum_eps``); times ``route_scale``
     out = sum over chosen of weight * expert(h)
 
-Outputs 0 .. num_experts - 1 are small gated feed-forwards with tensors ``e<i>.gate``, ``e<i>.up``, ``e<i>.down``:
-g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit), W_down (g * sigmoid(alpha * g) * (u + 1)).  The last
-``num_identity`` outputs are identity experts, expert(h) = h, without tensors.
+Outputs 0 .. num_experts - 1 are small gated feed-forwards with tensors ``e<i>.gate``, ``e<i>.up``, ``e<i>.down``.
+``activation`` "clamped_swish": g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit),
+W_down (g * sigmoid(alpha * g) * (u + 1)); "silu": W_down (silu(W_gate h) * W_up h).  The last ``num_identity`` outputs
+are identity experts, expert(h) = h, without tensors.
 
 Everything runs on the device (csrc/moe.cu): the router (logits, then selection), a sort of the (token, choice) pairs by expert, one product
 per tile of an expert's rows for gate-and-up (with the activation) and one for down, and the weighted sum.  The
@@ -25,16 +29,34 @@ from .base import FeedForward, ParamSpec, register_feed_forward, workspace_piece
 
 @register_feed_forward("routed_experts")
 class RoutedExperts(FeedForward):
+    ACTIVATIONS = ("clamped_swish", "silu")
+
     def __init__(self, hidden_size: int, expert_size: int, num_experts: int, num_identity: int, top: int, limit: float,
-                 dtype, device, alpha: float = 1.702):
+                 dtype, device, alpha: float = 1.702, activation: str = "clamped_swish", score: str = "softmax",
+                 correction: bool = True, groups: int = 1, keep_groups: int = 1, group_top: int = 1, normalize: bool = False,
+                 sum_eps: float = 0.0, route_scale: float = 1.0):
         if min(hidden_size, expert_size, num_experts, top) <= 0 or num_identity < 0:
             raise ValueError("routed_experts: sizes must be positive")
         if top > num_experts + num_identity:
             raise ValueError(f"routed_experts: {top} of {num_experts + num_identity} router outputs cannot be chosen")
         if not limit > 0:
             raise ValueError("routed_experts: limit must be positive")
+        if activation not in self.ACTIVATIONS or score not in ops.ROUTER_SCORES:
+            raise ValueError(f"routed_experts: activation one of {self.ACTIVATIONS}, score one of {sorted(ops.ROUTER_SCORES)}")
+        outputs = num_experts + num_identity
+        if groups < 1 or outputs % groups or not 1 <= keep_groups <= groups or not 1 <= group_top <= ops.ROUTER_GROUP_TOP_MAX:
+            raise ValueError(f"routed_experts: {outputs} router outputs in {groups} equal groups of which {keep_groups} stay, "
+                             f"a group's score from its {group_top} (at most {ops.ROUTER_GROUP_TOP_MAX}) best")
+        if top > outputs // groups * keep_groups:
+            raise ValueError(f"routed_experts: {top} choices do not fit the {keep_groups} groups that stay")
         self.hidden, self.ff, self.E, self.I, self.top = hidden_size, expert_size, num_experts, num_identity, top
-        self.limit, self.alpha = float(limit), float(alpha)
+        if activation == "silu":
+            self.limit, self.alpha, self.up_shift = float("inf"), 1.0, 0.0
+        else:
+            self.limit, self.alpha, self.up_shift = float(limit), float(alpha), 1.0
+        self.activation, self.score, self.has_correction = activation, score, bool(correction)
+        self.rule = dict(score=score, groups=int(groups), keep_groups=int(keep_groups), group_top=int(group_top),
+                         normalize=bool(normalize), sum_eps=float(sum_eps), scale=float(route_scale))
         self.dtype, self.device = dtype, device
         self.w_gate_up = self.w_down = self.w_router = self.correction = None
 
@@ -45,14 +67,15 @@ class RoutedExperts(FeedForward):
             specs[f"e{e}.up"] = ParamSpec((self.ff, self.hidden))
             specs[f"e{e}.down"] = ParamSpec((self.hidden, self.ff))
         specs["router"] = ParamSpec((self.E + self.I, self.hidden), "bias")       # held in float32: the router is
-        specs["correction"] = ParamSpec((self.E + self.I,), "bias")
+        if self.has_correction:
+            specs["correction"] = ParamSpec((self.E + self.I,), "bias")
         return specs
 
     def load_params(self, tensors):
         self.w_gate_up = torch.stack([torch.cat([tensors[f"e{e}.gate"], tensors[f"e{e}.up"]], dim=0) for e in range(self.E)]).contiguous()
         self.w_down = torch.stack([tensors[f"e{e}.down"] for e in range(self.E)]).contiguous()
         self.w_router = tensors["router"].contiguous()
-        self.correction = tensors["correction"].contiguous()
+        self.correction = tensors["correction"].contiguous() if self.has_correction else None
 
     def product_weights(self):
         return []                 # the experts' products are this part's own kernels; nothing to measure or tile
@@ -78,11 +101,11 @@ class RoutedExperts(FeedForward):
         tile_expert, tile_row0, tile_rows = (ws.take((tiles,), torch.int32) for _ in range(3))
         meta = ws.take((4,), torch.int32)
         logits = ws.take((n, self.E + self.I), torch.float32)
-        ops.moe_router(x, self.w_router, self.correction, ids, weights, logits)
+        ops.moe_router(x, self.w_router, self.correction, ids, weights, logits, **self.rule)
         ops.moe_sort(ids, self.E, tm, sorted_token, pos, tile_expert, tile_row0, tile_rows, meta)
         act = ws.take((pairs, self.ff), self.dtype)
         lists = (sorted_token, tile_expert, tile_row0, tile_rows, meta, tiles, tm)
-        ops.moe_expert_gemm(x, self.w_gate_up, act, *lists, gated=True, limit=self.limit, alpha=self.alpha)
+        ops.moe_expert_gemm(x, self.w_gate_up, act, *lists, gated=True, limit=self.limit, alpha=self.alpha, up_shift=self.up_shift)
         y = ws.take((pairs, self.hidden), torch.float32)
         ops.moe_expert_gemm(act, self.w_down, y, *lists, gated=False)
         ops.moe_combine(y, x, pos, weights, out)

@@ -74,6 +74,44 @@ class ScalarRMSNorm(Norm):
         ops.gated_norm_residual(y, gate, gate_bias, self.gain, residual, plain, mult * self.out_scale, self.eps)
 
 
+@register_norm("layernorm")
+class LayerNorm(Norm):
+    """y = (x - mean(x)) / sqrt(var(x) + eps) * w + b, the variance the mean of the squared deviations; statistics in
+    float32.  ``tensor_name`` is the local name of the gain ("": the slot's prefix itself), the bias is that name plus
+    ``bias_suffix``.  ``out_scale`` multiplies what the norm returns (a model that scales its logits puts the factor
+    here: the output product is linear).  ``forward_streams`` reads a residual stream kept as several copies."""
+
+    def __init__(self, size: int, eps: float, dtype, device, tensor_name: str = "weight", bias_suffix: str = ".b",
+                 bias_name: str = "", out_scale: float = 1.0):
+        if size <= 0 or not eps > 0:
+            raise ValueError(f"layernorm: size {size} and eps {eps} must be positive")
+        self.size, self.eps, self.out_scale = size, float(eps), float(out_scale)
+        self.tensor_name = tensor_name
+        self.bias_name = bias_name or tensor_name + bias_suffix
+        self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+        self._one: Optional[torch.Tensor] = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {self.tensor_name: ParamSpec((self.size,), "gain"), self.bias_name: ParamSpec((self.size,), "bias")}
+
+    def load_params(self, tensors):
+        self.weight, self.bias = tensors[self.tensor_name].contiguous(), tensors[self.bias_name].contiguous()
+        self._one = torch.ones(1, dtype=torch.float32, device=self.weight.device)
+
+    def forward_streams(self, streams, coef, out, row_index=None):
+        """out = norm(sum_s coef[s] streams[s]); streams float32 [S, n, size]."""
+        ops.stream_norm(streams, coef, self.weight, self.bias, out, self.eps, row_index, self.out_scale)
+
+    def forward(self, residual, delta, out, row_index=None):
+        x = residual.unsqueeze(0)
+        if delta is not None:
+            if row_index is not None:
+                raise ValueError("layernorm: a pending addition cannot be made on gathered rows")
+            ops.stream_join(x, delta, self._one, self._one)
+        ops.stream_norm(x, self._one, self.weight, self.bias, out, self.eps, row_index, self.out_scale)
+
+
 @register_norm("none")
 class NoNorm(Norm):
     """Fills the norm slot of a sublayer that a layer does not have."""

@@ -79,7 +79,7 @@ def check_names_and_shapes(expected: Dict[str, object], present: Dict[str, Tuple
 def _place(t: torch.Tensor, role: str, compute_dtype: torch.dtype, device) -> torch.Tensor:
     if role == "matrix":
         target = compute_dtype
-    elif role in ("bias", "gain", "offset_gain"):
+    elif role in ("bias", "gain", "offset_gain", "identity"):
         target = torch.float32
     elif t.dtype.is_floating_point:
         target = torch.float32 if (t.dtype == torch.float32 or compute_dtype == torch.float32) else torch.bfloat16

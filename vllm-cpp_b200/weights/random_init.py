@@ -112,7 +112,7 @@ def normal_values(key: int, first: int, count: int, mean: float, std: float) -> 
 
 
 def _mean_std(role: str, std: float, gain_std: float):
-    if role == "offset_gain":
+    if role in ("offset_gain", "identity"):
         return 0.0, gain_std
     return (1.0, gain_std) if role == "gain" else (0.0, std)
 
@@ -129,8 +129,16 @@ def random_tensor(name: str, shape, role: str, seed: int, std: float, gain_std: 
         from ..csrc import ops
         out = torch.empty(shape, dtype=dtype, device=device)
         ops.random_normal(out, key, mean, sd)
-        return out
-    return torch.from_numpy(normal_values(key, 0, numel, mean, sd)).view(shape).to(dtype)
+        return _plus_identity(out) if role == "identity" else out
+    out = torch.from_numpy(normal_values(key, 0, numel, mean, sd)).view(shape)
+    return (_plus_identity(out) if role == "identity" else out).to(dtype)
+
+
+def _plus_identity(t: torch.Tensor) -> torch.Tensor:
+    """A square matrix drawn around zero becomes one drawn around the identity (role "identity")."""
+    if t.dim() != 2 or t.shape[0] != t.shape[1]:
+        raise ValueError(f"role 'identity' is for square matrices, got {tuple(t.shape)}")
+    return (t.float() + torch.eye(t.shape[0], dtype=torch.float32, device=t.device)).to(t.dtype)
 
 
 def random_rows(name: str, shape, rows, role: str, seed: int, std: float, gain_std: float) -> np.ndarray:
