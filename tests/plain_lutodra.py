@@ -388,10 +388,27 @@ def tensor_shapes(cfg, rank=DEFAULT_RANK):
     return shapes
 
 
-def random_weights(cfg, seed, sharp=1.0, rank=DEFAULT_RANK):
+def static_levels(rng, router, floor=0.04):
+    """Router levels (one logit per expert, in an order drawn at random) whose decisions between groups and between
+    experts all have a clear margin in score space."""
+    E, top = router["experts"], router["top"]
+    step = min(0.35, 5.0 / E)
+    for _ in range(200):
+        c = rng.permutation((np.arange(E) - (E - 1) / 2.0) * step + rng.uniform(-0.1, 0.1, E) * step)
+        margins = []
+        route({"x.router": c[:, None]}, "x.", router, np.ones((1, 1)), margins)
+        if not margins or min(margins) > floor:
+            return c
+    raise AssertionError("no router levels with clear margins found")
+
+
+def random_weights(cfg, seed, sharp=1.0, rank=DEFAULT_RANK, decisive_routing=False):
     """Weights that keep the residual stream of order one and make every mechanism matter: peaked attention (``sharp``
     scales the query and key gains), sinks around the scores' size, decays spread between fast and slow, mixing
-    matrices near the identity with visible off-diagonal parts, biases that are not zero."""
+    matrices near the identity with visible off-diagonal parts, biases that are not zero.  ``decisive_routing``: the
+    routers' inputs get a coordinate that is always 1 (gain 0, bias 1 in the norm before) and the routers read mostly
+    that, every expert at a level of its own, so that no rounding of the input turns a choice (for 16-bit runs; what
+    follows the input is covered by the 32-bit runs and the router's own test)."""
     rng = np.random.default_rng(seed)
     D = cfg["width"]
     w = {}
@@ -433,4 +450,12 @@ def random_weights(cfg, seed, sharp=1.0, rank=DEFAULT_RANK):
         else:
             a = rng.standard_normal(shape) / math.sqrt(fan_in)
         w[name] = a.astype(np.float64)
+    if decisive_routing:
+        for i, layer in enumerate(cfg["layers"]):
+            mlp = layer.get("mlp")
+            if mlp and mlp["kind"] == "moe":
+                w[f"l{i}.norm2"][0], w[f"l{i}.norm2.b"][0] = 0.0, 1.0
+                r = 0.01 / math.sqrt(D) * rng.standard_normal((mlp["router"]["experts"], D))
+                r[:, 0] = static_levels(rng, mlp["router"])
+                w[f"l{i}.mlp.router"] = r
     return w

@@ -103,7 +103,7 @@ VCB_EXPORT int vcb_causal_conv(const void* x, long long ldx, const float* pre_bi
                                const int* state_slots, int n_reqs, int max_q_len, int C, int J, int act, int dtype,
                                void* stream) {
     if (n_reqs <= 0 || max_q_len <= 0) return 0;
-    if (!x || !w || !state || !out || C <= 0 || J <= 0 || J > CONV_MAX_TAPS || n_reqs > 65535) return VCB_ERR_BAD_ARG;
+    if (!x || !w || (!state && J > 1) || !out || C <= 0 || J <= 0 || J > CONV_MAX_TAPS || n_reqs > 65535) return VCB_ERR_BAD_ARG;
     ConvArgs a{x, ldx, pre_bias, w, bias, state, slot_stride, out, ldo, q_start, state_slots, C, J, act};
     dim3 grid((max_q_len + CONV_SEG - 1) / CONV_SEG, n_reqs, (C + 127) / 128);
     if (grid.z > 65535) return VCB_ERR_UNSUPPORTED;
