@@ -359,17 +359,19 @@ def test_a_key_written_long_before_it_is_asked_for(H, G, dk, dv, planted_at, cut
     rows_close(got.reshape(n, -1), want.reshape(n, -1), 3e-5, "planted key")
 
 
-@pytest.mark.parametrize("dtype,H,G,dk,dv,rotation,page", [
-    ("float32", 4, 2, 32, 16, rot(16, 300.0, (8.0, 1.0, 3.0, 48)), 16), ("float32", 3, 3, 24, 40, None, 16),
-    ("float32", 2, 1, 8, 8, rot(8, 20.0), 32), ("bfloat16", 6, 2, 64, 64, rot(32, 1e4, (5.0, 1.0, 3.0, 128)), 16),
-    ("bfloat16", 2, 1, 128, 128, rot(128, 1e5), 32), ("bfloat16", 5, 1, 48, 80, rot(24, 50.0, (2.0, 0.5, 8.0, 16)), 16),
-    ("float32", 8, 8, 16, 16, rot(2, 7.0), 16)])
-def test_attention_with_a_sink_and_a_planted_key(dtype, H, G, dk, dv, rotation, page):
+@pytest.mark.parametrize("dtype,H,G,dk,dv,rotation,page,plain_kernel", [
+    ("float32", 4, 2, 32, 16, rot(16, 300.0, (8.0, 1.0, 3.0, 48)), 16, True), ("float32", 3, 3, 24, 40, None, 16, True),
+    ("float32", 2, 1, 8, 8, rot(8, 20.0), 32, True), ("bfloat16", 6, 2, 64, 64, rot(32, 1e4, (5.0, 1.0, 3.0, 128)), 16, False),
+    ("bfloat16", 6, 2, 64, 64, rot(32, 1e4, (5.0, 1.0, 3.0, 128)), 16, True), ("bfloat16", 2, 1, 128, 128, rot(128, 1e5), 32, False),
+    ("bfloat16", 20, 1, 64, 64, None, 16, False), ("bfloat16", 4, 4, 128, 128, rot(64, 500.0), 16, False),
+    ("bfloat16", 5, 1, 48, 80, rot(24, 50.0, (2.0, 0.5, 8.0, 16)), 16, True), ("float32", 8, 8, 16, 16, rot(2, 7.0), 16, True)])
+def test_attention_with_a_sink_and_a_planted_key(dtype, H, G, dk, dv, rotation, page, plain_kernel):
     """The mixer itself (its products are identities, so its input rows are q, k, v and the gate's logits) through the
     cache manager's pages, two requests, portions beside single tokens across page borders.  Request "a" has one key
     near its start that the queries of its last tokens point at (in the coordinates that no rotation turns): a key far
     away, among hundreds, carries most of their weight.  The sinks are as large as the largest scores, so a sink that is
-    left out, scaled, or counted per key shows; every head has its own."""
+    left out, scaled, or counted per key shows; every head has its own.  bfloat16 heads of 64 and 128 run the tensor-core
+    kernels (a portion's tiles, single tokens in splits that are merged) unless the case asks for the plain one."""
     from vllm_cpp_b200.config.model_spec import PartSpec
     from vllm_cpp_b200.parts import model as _registers_every_part  # noqa: F401
     from vllm_cpp_b200.parts.sink_attention import SinkAttention
@@ -390,6 +392,10 @@ def test_attention_with_a_sink_and_a_planted_key(dtype, H, G, dk, dv, rotation, 
          p + "k.norm": stored((1 + 0.1 * rng.standard_normal(dk)) * sharp / dk ** 0.25, "bfloat16"),
          p + "sink": stored(4.0 + 2.0 * rng.standard_normal(H), "bfloat16")}
     att_.load_params(part_weights(w, p, dtype))
+    if plain_kernel:
+        att_._tensor_core_path = lambda: False
+    else:
+        assert att_._tensor_core_path()
     x = {r: rng.standard_normal((n, width)) for r, n in (("a", T), ("b", 90))}
     unrot = slice(rotation["dims"] if rotation else 0, dk) if (rotation is None or rotation["dims"] < dk) else None
     if unrot is not None:

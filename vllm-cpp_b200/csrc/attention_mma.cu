@@ -62,7 +62,20 @@ struct MmaAttnArgs {
     float cap;
     const float* bias_t;           // [nh][bias_len]: a head's bias by distance, contiguous
     int bias_len;
+    // The output's epilogue (null: none).  sink[head]: a logit in natural units that joins the softmax's denominator once,
+    // unscaled, with no key and no value.  gate[token * ldg + head]: the head's output is multiplied by sigmoid(gate).
+    const float* sink;
+    const __nv_bfloat16* gate;
+    long long ldg;
 };
+
+// 1 / (l + e^(sink - m)) * sigmoid(gate): what an output row is multiplied by.  m2: the reference of l in units of log2.
+__device__ __forceinline__ float epilogue_factor(const MmaAttnArgs& a, float l, float m2, size_t token, int head) {
+    if (a.sink && m2 != -INFINITY) l += exp2f(fmaf(a.sink[head], 1.4426950408889634f, -m2));
+    float inv = l > 0.0f ? 1.0f / l : 0.0f;
+    if (a.gate) inv *= 1.0f / (1.0f + __expf(-__bfloat162float(a.gate[token * (size_t)a.ldg + head])));
+    return inv;
+}
 
 // Shaped scores.  cap * tanh(x / cap) = cap - 2 cap / (1 + e^(2 x / cap)): one multiplication into the exponent's
 // units, ex2, an addition, a reciprocal and one multiply-add (ex2.approx and rcp.approx are good to 2^-22 relative:
@@ -472,7 +485,7 @@ attention_decode_kernel(MmaAttnArgs a) {
             }
             const int head = g * G + mt * 16 + row;
             if (nsplit == 1) {
-                const float inv = 1.0f / l;
+                const float inv = epilogue_factor(a, l, mx, (size_t)t, head);
                 uint2 packed = make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
                 *reinterpret_cast<uint2*>(a.out + ((size_t)t * a.nh + head) * D + dim) = packed;
             } else {
@@ -519,7 +532,7 @@ attention_decode_kernel(MmaAttnArgs a) {
             total += m_l.y * f;
             acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
         }
-        const float inv = 1.0f / total;
+        const float inv = epilogue_factor(a, total, mx, (size_t)t, head);
         uint2 packed = make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
         *reinterpret_cast<uint2*>(a.out + ((size_t)t * a.nh + head) * D + dim) = packed;
     }
@@ -968,8 +981,8 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
             if (!cx_mbar_wait(B(O_DONE), 0)) ok = false;       // the last P V
             fence_after();
             if (ok) {
-                const float inv = l > 0.0f ? 1.0f / l : 0.0f;
                 const int prc = min(pr, rows_total - 1);
+                const float inv = epilogue_factor(a, l, m_ref == -INFINITY ? -INFINITY : m_ref * sl2, (size_t)(q0 + prc / G), g * G + prc % G);
                 __nv_bfloat16* dst = a.out + ((size_t)(q0 + prc / G) * a.nh + g * G + prc % G) * D;
 #pragma unroll 1
                 for (int c0 = 0; c0 < D; c0 += 32) {
@@ -1037,13 +1050,14 @@ VCB_EXPORT int vcb_attention_decode_mma_planes(const void* q, const void* cache,
     return d == 64 ? launch_decode<64>(a, n_list, nsplit, s) : launch_decode<128>(a, n_list, nsplit, s);
 }
 
-// The same with shaped scores (see MmaAttnArgs): cap <= 0 no cap, bias_t null no bias.
+// The same with shaped scores and an epilogue (see MmaAttnArgs): cap <= 0 no cap; bias_t, sink, gate null: none.
 VCB_EXPORT int vcb_attention_decode_mma_shaped(const void* q, const void* cache, void* out, const int* q_start,
                                                const int* ctx_lens, const int* block_table, int bt_stride,
                                                const int* req_list, int n_list, int nsplit, float* part_o,
                                                float* part_ml, int* counters, const int* split_tiles, int nh, int nkv,
                                                int d, int page, int window, float scale, int num_pages, int* status,
-                                               int kv_share, float cap, const float* bias_t, int bias_len, void* stream) {
+                                               int kv_share, float cap, const float* bias_t, int bias_len, const float* sink,
+                                               const void* gate, long long ldg, void* stream) {
     if (n_list <= 0) return 0;
     int c = check_common(nh, nkv, d, page, window, num_pages);
     if (c) return c;
@@ -1051,7 +1065,7 @@ VCB_EXPORT int vcb_attention_decode_mma_shaped(const void* q, const void* cache,
     if (nsplit < 1 || nsplit > 32 || (nsplit > 1 && (!part_o || !part_ml || !counters))) return VCB_ERR_BAD_ARG;
     MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
                   block_table, req_list, nullptr, part_o, part_ml, counters, status, split_tiles, bt_stride, nh, nkv,
-                  page, window, scale, num_pages, 2, kv_share, cap, bias_t, bias_len};
+                  page, window, scale, num_pages, 2, kv_share, cap, bias_t, bias_len, sink, (const __nv_bfloat16*)gate, ldg};
     cudaStream_t s = (cudaStream_t)stream;
     return d == 64 ? launch_decode<64>(a, n_list, nsplit, s) : launch_decode<128>(a, n_list, nsplit, s);
 }
@@ -1085,19 +1099,20 @@ VCB_EXPORT int vcb_attention_prefill_tc_planes(const void* q, const void* cache,
     return d == 64 ? launch_prefill_tc<64>(a, n_tiles, (cudaStream_t)stream) : launch_prefill_tc<128>(a, n_tiles, (cudaStream_t)stream);
 }
 
-// The same with shaped scores (see MmaAttnArgs).
+// The same with shaped scores and an epilogue (see MmaAttnArgs).
 VCB_EXPORT int vcb_attention_prefill_tc_shaped(const void* q, const void* cache, void* out, const int* q_start,
                                                const int* ctx_lens, const int* block_table, int bt_stride,
                                                const int* tile_req, const int* tile_row0, int n_tiles, int nh,
                                                int nkv, int d, int page, int window, float scale, int num_pages,
-                                               int* status, float cap, const float* bias_t, int bias_len, void* stream) {
+                                               int* status, float cap, const float* bias_t, int bias_len, const float* sink,
+                                               const void* gate, long long ldg, void* stream) {
     if (n_tiles <= 0) return 0;
     int c = check_common(nh, nkv, d, page, window, num_pages);
     if (c) return c;
     if (bias_t && bias_len <= 0) return VCB_ERR_BAD_ARG;
     MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
                   block_table, tile_req, tile_row0, nullptr, nullptr, nullptr, status, nullptr, bt_stride, nh, nkv, page,
-                  window, scale, num_pages, 2, 1, cap, bias_t, bias_len};
+                  window, scale, num_pages, 2, 1, cap, bias_t, bias_len, sink, (const __nv_bfloat16*)gate, ldg};
     return d == 64 ? launch_prefill_tc<64>(a, n_tiles, (cudaStream_t)stream) : launch_prefill_tc<128>(a, n_tiles, (cudaStream_t)stream);
 }
 

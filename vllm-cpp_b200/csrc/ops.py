@@ -54,8 +54,9 @@ _SIGNATURES = {
     "vcb_latent_cache_write": [_P, _I, _P, _P, _P, _P, _I, _P, ctypes.c_longlong, _I, _I, _I, _F, _I, _P, _I, _P],
     "vcb_headwise_linear": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "vcb_sigmoid_gate": [_P, _P, _I, _I, _I, _I, _I, _P],
-    "vcb_attention_decode_mma_shaped": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _I, _F, _P, _I, _P],
-    "vcb_attention_prefill_tc_shaped": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _F, _P, _I, _P],
+    "vcb_attention_decode_mma_shaped": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _I, _F, _P, _I,
+                                        _P, _P, _L, _P],
+    "vcb_attention_prefill_tc_shaped": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _F, _P, _I, _P, _P, _L, _P],
     "vcb_embedding_scaled": [_P, _P, _P, _I, _I, _I, _P, _F, _I, _P],
     "vcb_norm_residual_norm": [_P, _P, _P, _P, _P, _I, _I, _F, _F, _I, _P],
     "vcb_decayed_state_scan": [_P, _P, _P, _P, _L, _L, _L, _L, _P, _P, _F, _F, _I, _P, _P, _L, _P, _P, _I, _I, _I, _I, _I, _P, _L, _P, _I, _P],
@@ -270,10 +271,22 @@ DECODE_KEY_TILE = 64          # keys per tile of the decode kernel
 DECODE_MAX_SPLITS = 32
 
 
+def _epilogue_args(sink, head_gate, n_tokens: int, num_heads: int, what: str) -> None:
+    _need(sink is None or (sink.dtype == torch.float32 and sink.numel() == num_heads and sink.is_contiguous()), f"{what}: sink float32 [heads]")
+    _need(head_gate is None or (head_gate.dtype == torch.bfloat16 and head_gate.shape == (n_tokens, num_heads) and head_gate.stride(1) == 1),
+          f"{what}: head_gate bfloat16 [tokens, heads] with unit inner stride")
+
+
+def _epilogue_ptrs(sink, head_gate):
+    return (None if sink is None else sink.data_ptr(), None if head_gate is None else head_gate.data_ptr(),
+            0 if head_gate is None else head_gate.stride(0))
+
+
 def attention_decode_mma(q, cache, out, q_start, ctx_lens, block_table, req_list, n_list: int, nsplit: int,
                          part_o, part_ml, counters, *, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
                          window: int, scale: float, split_tiles=None, planes: int = 2, kv_share: int = 1,
-                         cap: float = 0.0, bias_t: Optional[torch.Tensor] = None) -> None:
+                         cap: float = 0.0, bias_t: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None,
+                         head_gate: Optional[torch.Tensor] = None) -> None:
     """Split-KV tensor-core attention for requests that bring one token each (bfloat16).  The grid has
     ``nsplit`` columns; without ``split_tiles`` every request's keys are cut into that many equal parts,
     with it (int32 [1] on the device: tiles of DECODE_KEY_TILE keys per split) a request takes as many
@@ -291,10 +304,12 @@ def attention_decode_mma(q, cache, out, q_start, ctx_lens, block_table, req_list
               "attention_decode_mma: scratch for the split merge is too small")
     _need(planes in (1, 2), "planes must be 1 or 2")
     _need(kv_share >= 1 and num_kv_heads % kv_share == 0, "attention_decode_mma: kv_share divides num_kv_heads")
-    if cap > 0 or bias_t is not None:
-        # shaped scores: cap * tanh(scale * q.k / cap) + bias_t[head, min(distance, last)] (see attention_mma.cu)
+    if cap > 0 or bias_t is not None or sink is not None or head_gate is not None:
+        # shaped scores: cap * tanh(scale * q.k / cap) + bias_t[head, min(distance, last)]; the epilogue: a sink logit per
+        # head in the denominator, the head's output times sigmoid(head_gate[token, head]) (see attention_mma.cu)
         _need(planes == 2, "attention_decode_mma: shaped scores come with keys and values in planes of their own")
         _need(bias_t is None or (bias_t.dim() == 2 and bias_t.shape[0] == num_heads), "attention_decode_mma: bias_t [heads, distances]")
+        _epilogue_args(sink, head_gate, q.shape[0], num_heads, "attention_decode_mma")
         _check(lib().vcb_attention_decode_mma_shaped(
             _dev(q, "q"), _dev(cache, "cache"), _dev(out, "out"), _dev(q_start, "q_start", torch.int32),
             _dev(ctx_lens, "ctx_lens", torch.int32), _dev(block_table, "block_table", torch.int32),
@@ -306,7 +321,7 @@ def attention_decode_mma(q, cache, out, q_start, ctx_lens, block_table, req_list
             num_heads, num_kv_heads, head_dim, page_size, window, float(scale), cache.shape[0],
             status_tensor(q.device).data_ptr(), kv_share, float(cap),
             None if bias_t is None else _dev(bias_t, "bias_t", torch.float32), 0 if bias_t is None else bias_t.shape[1],
-            _stream()), "attention_decode_mma")
+            *_epilogue_ptrs(sink, head_gate), _stream()), "attention_decode_mma")
         return
     _check(lib().vcb_attention_decode_mma_planes(
         _dev(q, "q"), _dev(cache, "cache"), _dev(out, "out"), _dev(q_start, "q_start", torch.int32),
@@ -337,7 +352,8 @@ TC_ATTENTION_TILE_ROWS = 128     # packed rows per tile of its work list
 
 def attention_prefill_tc(q, cache, out, q_start, ctx_lens, block_table, tile_req, tile_row0, *,
                          num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int,
-                         scale: float, planes: int = 2, cap: float = 0.0, bias_t: Optional[torch.Tensor] = None) -> None:
+                         scale: float, planes: int = 2, cap: float = 0.0, bias_t: Optional[torch.Tensor] = None,
+                         sink: Optional[torch.Tensor] = None, head_gate: Optional[torch.Tensor] = None) -> None:
     """Attention for portions of any length on tcgen05 tensor cores (scores and output tiles in tensor
     memory); head sizes 64 and 128, bfloat16, pages of a multiple of 8 slots, tiles of 128 packed rows."""
     _need(q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
@@ -347,16 +363,17 @@ def attention_prefill_tc(q, cache, out, q_start, ctx_lens, block_table, tile_req
     n_tiles = tile_req.numel()
     _need(tile_row0.numel() == n_tiles, "one first row per tile")
     _need(planes in (1, 2), "planes must be 1 or 2")
-    if cap > 0 or bias_t is not None:
+    if cap > 0 or bias_t is not None or sink is not None or head_gate is not None:
         _need(planes == 2, "attention_prefill_tc: shaped scores come with keys and values in planes of their own")
         _need(bias_t is None or (bias_t.dim() == 2 and bias_t.shape[0] == num_heads), "attention_prefill_tc: bias_t [heads, distances]")
+        _epilogue_args(sink, head_gate, q.shape[0], num_heads, "attention_prefill_tc")
         _check(lib().vcb_attention_prefill_tc_shaped(
             _dev(q, "q"), _dev(cache, "cache"), _dev(out, "out"), _dev(q_start, "q_start", torch.int32),
             _dev(ctx_lens, "ctx_lens", torch.int32), _dev(block_table, "block_table", torch.int32),
             block_table.shape[1], _dev(tile_req, "tile_req", torch.int32), _dev(tile_row0, "tile_row0", torch.int32),
             n_tiles, num_heads, num_kv_heads, head_dim, page_size, window, float(scale), cache.shape[0],
             status_tensor(q.device).data_ptr(), float(cap), None if bias_t is None else _dev(bias_t, "bias_t", torch.float32),
-            0 if bias_t is None else bias_t.shape[1], _stream()), "attention_prefill_tc")
+            0 if bias_t is None else bias_t.shape[1], *_epilogue_ptrs(sink, head_gate), _stream()), "attention_prefill_tc")
         return
     _check(lib().vcb_attention_prefill_tc_planes(
         _dev(q, "q"), _dev(cache, "cache"), _dev(out, "out"), _dev(q_start, "q_start", torch.int32),

@@ -127,13 +127,17 @@ class PagedAttentionKernels(Mixer):
 
     def score_shaping(self) -> dict:
         """What the tensor-core kernels do to a score beyond the scale: ``cap`` (cap * tanh(score / cap)) and ``bias_t``
-        (float32 [heads, distances], added by distance); empty for plain scaled scores."""
+        (float32 [heads, distances], added by distance), and to the softmax: ``sink`` (float32 [heads], a logit that joins the
+        denominator once); empty for plain scaled scores."""
         return {}
 
-    def attend(self, q, attn, step, cache, block_table):
+    def attend(self, q, attn, step, cache, block_table, head_gate=None):
+        """``head_gate`` (tensor-core kernels only): logits [tokens, heads]; a head's output is multiplied by their sigmoid."""
         if self._tensor_core_path():
             kw = dict(num_heads=self.nh, num_kv_heads=self.nkv, head_dim=self.d, page_size=cache.page_size,
                       window=self.window, scale=self.scale, planes=self.planes, **self.score_shaping())
+            if head_gate is not None:
+                kw["head_gate"] = head_gate
             if step.decode_only:
                 nsplit = step.shapes.get(self._splits_key())
                 split_tiles = step.extras.get(self._splits_key())
@@ -160,6 +164,8 @@ class PagedAttentionKernels(Mixer):
                 tiles = step.extras[f"attn_tiles_g{self.nh // self.nkv}"]
                 ops.attention_prefill_tc(q, cache.pages, attn, step.q_start, step.ctx_lens, block_table, tiles[0], tiles[1], **kw)
             return
+        if head_gate is not None:
+            raise ValueError("attend: the plain kernel has no gate; a mixer with one calls its own kernel")
         ops.attention_simt(q, cache.pages, attn, step.positions, step.req_of_token, block_table,
                            num_heads=self.nh, num_kv_heads=self.nkv, head_dim=self.d,
                            page_size=cache.page_size, window=self.window, scale=self.scale, planes=self.planes)

@@ -8,8 +8,10 @@
 
 The sink is a learned logit per head that takes part in the denominator only: it has no key and no value, is not
 scaled, and counts once.  ``window`` > 0 restricts the keys to the last ``window``.  q, k, v and the gate are one product;
-norm, rotation and the cache write are one kernel (csrc/attention_biased.cu, qk_head_rope_cache_write_kernel); attention
-runs the plain paged kernel of that file with the sink and the gate in its epilogue.  The cache holds rows of
+norm, rotation and the cache write are one kernel (csrc/attention_biased.cu, qk_head_rope_cache_write_kernel); bfloat16
+heads of 64 or 128 with keys as wide as values run the tensor-core kernels (csrc/attention_mma.cu: tcgen05 for portions,
+split-KV for single tokens) with the sink and the gate in their epilogues, everything else the plain paged kernel of
+attention_biased.cu, which has them too.  The cache holds rows of
 max(head_dim, v_head_dim) elements.  The reference's attention (src/layers/attention.cpp) has rotation and none of the
 rest.
 """
@@ -53,7 +55,11 @@ class SinkAttention(PagedAttentionKernels):
         self.w_in = self.w_o = self.w_qn = self.w_kn = self.sink = None
 
     def _tensor_core_path(self) -> bool:
-        return False              # the sink lives in the plain kernel's epilogue
+        # bfloat16 heads of 64 and 128 with keys as wide as values: the tensor-core kernels, sink and gate in their epilogues
+        return self.dk == self.dv and super()._tensor_core_path()
+
+    def score_shaping(self):
+        return {"sink": self.sink} if self.has_sink else {}
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         specs = {"q": ParamSpec((self.nh * self.dk, self.hidden)), "k": ParamSpec((self.nkv * self.dk, self.hidden)),
@@ -76,6 +82,8 @@ class SinkAttention(PagedAttentionKernels):
             self.w_qn, self.w_kn = tensors["q.norm"].contiguous(), tensors["k.norm"].contiguous()
         if self.has_sink:
             self.sink = tensors["sink"].contiguous()
+        if self.dk == self.dv:
+            self.warn_if_plain()
 
     def tensors(self):
         return super().tensors() + self.position.tensors()
@@ -110,7 +118,10 @@ class SinkAttention(PagedAttentionKernels):
                                      step.req_of_token, block_table, eps=self.eps, write_kv=writes_cache, **sizes)
         attn = ws.take((n, self.nh * self.dv), self.dtype)
         gate = proj[:, g_off:] if self.head_gate else None
-        ops.attention_biased(q, pages, attn, gate, step.positions, step.req_of_token, block_table, None, window=self.window,
-                             scale=self.scale, cap=0.0, sink=self.sink, gate_per_head=True, **sizes)
+        if self._tensor_core_path() and cache.page_size % 8 == 0:
+            self.attend(q, attn, step, cache, block_table, head_gate=gate)
+        else:
+            ops.attention_biased(q, pages, attn, gate, step.positions, step.req_of_token, block_table, None, window=self.window,
+                                 scale=self.scale, cap=0.0, sink=self.sink, gate_per_head=True, **sizes)
         ops.linear(attn, self.w_o, out)
         ws.release(mark)
