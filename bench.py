@@ -987,6 +987,258 @@ def retodra_kernels(z, peaks):
     return rows
 
 
+# ------------------------------------------------------------------- the Lutodra design beside Retodra
+# Layer sizes that resemble real models'.  Lutodra: a real-gated linear recurrent unit with a dense feed-forward, attention
+# with sinks and routed experts, the gated delta rule with a dense feed-forward, attention again; four residual streams.
+# Retodra (recurrent layers in turn with attention layers, dense and routed feed-forwards) at equal width, heads, head
+# size, feed-forward widths and experts is the nearest model the engine has; its attention has a window, Lutodra's has not.
+LUTODRA_SIZES = {"2k": dict(width=2048, heads=16, kv_heads=4, dim=128, ff=8192, experts=16, top=2, expert_ff=2048, layers=4, streams=4),
+                 "4k": dict(width=4096, heads=32, kv_heads=8, dim=128, ff=14336, experts=32, top=4, expert_ff=2048, layers=4, streams=4)}
+LUTODRA_VOCAB, LUTODRA_CONTEXT, LUTODRA_PROMPT = 32000, 2048, 2048
+
+
+def lutodra_configs(size):
+    z = LUTODRA_SIZES[size]
+    w, h = z["width"], z["heads"]
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]},
+           "router": {"experts": z["experts"], "top": z["top"], "scale": 2.5, "groups": {"count": 4, "keep": 2}}}
+    att = {"type": "attention", "mlp": moe,
+           "mixer": {"heads": h, "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
+                     "rot": {"base": 1e6, "dims": z["dim"] // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}}
+    rec = {"type": "rglru", "mixer": {"width": w, "blocks": h, "conv": 4}, "mlp": dense}
+    dlt = {"type": "channel_delta", "mixer": {"heads": h, "kv_heads": h // 2, "dim": 128, "vdim": w // h, "conv": 4}, "mlp": dense}
+    lutodra = {"architecture": "Lutodra", "vocab": LUTODRA_VOCAB, "width": w, "streams": z["streams"], "norm": {"eps": 1e-6},
+               "logit_scale": 1.0, "layers": [dict((rec, att, dlt, att)[i % 4]) for i in range(z["layers"])]}
+    return lutodra
+
+
+def run_lutodra(a) -> int:
+    """Prefill and decode throughput of the Lutodra design beside Retodra at equal layer sizes (random weights, synthetic
+    cache contents), and the design's own kernels alone beside the like kernels of the engine's other models with their
+    share of the measured peaks.  One JSON line."""
+    import numpy as np
+    peaks = load_peaks()
+    steps, warmup = max(1, a.steps), max(3, a.warmup)
+    rng = np.random.default_rng(0)
+    sampler = ClockSampler()
+    sampler.start()
+    sampler.mark("decode")
+    out = {"metric": "prefill and decode tok/s of Lutodra beside Retodra at equal layer sizes (bf16, random weights)",
+           "n_gpus": 1, "steps": steps, "warmup": warmup, "dtype": "bf16", "data": "synthetic", "sizes": {}, "peaks": peaks}
+    sizes = a.lutodra.split(",") if a.lutodra != "all" else sorted(LUTODRA_SIZES)
+    for size in sizes:
+        args = (steps, warmup, rng, peaks, LUTODRA_VOCAB, LUTODRA_CONTEXT, LUTODRA_PROMPT)
+        out["sizes"][size] = {"layers": LUTODRA_SIZES[size], "lutodra": measure_design(lutodra_configs(size), (8, 64), *args),
+                              "retodra": measure_design(retodra_configs(size)[0], (8, 64), *args)}
+    if not a.skip_points:
+        out["kernels"] = lutodra_kernels(LUTODRA_SIZES[sizes[-1]], peaks)
+    out["clocks"] = sampler.stop()
+    big = out["sizes"][sizes[-1]]
+    out.update(value=big["lutodra"]["decode"]["8"]["tok_s"], unit=f"tokens/s (Lutodra, {sizes[-1]}-wide layers, batch 8)",
+               higher_is_better=True, gpu_launches=big["lutodra"]["decode"]["8"]["launches_per_step"] * steps,
+               config={"sizes": LUTODRA_SIZES, "context": LUTODRA_CONTEXT, "prompt": LUTODRA_PROMPT,
+                       "retodra_window": RETODRA_WINDOW, "l2": "a step's weights exceed the 126 MB of L2"})
+    print(json.dumps(out))
+    return 0
+
+
+def lutodra_kernels(z, peaks):
+    """The design's own kernels alone at one layer size, each beside the like kernel of another model of the engine:
+    [{kernel, like, us, GB/s or TFLOP/s, share of the measured peak}, ...] (CUDA graphs on rotating buffers)."""
+    import numpy as np
+    import torch
+    from vllm_cpp_b200.csrc import ops
+    h, nh, nkv, d, S, page, bf, dev = z["width"], z["heads"], z["kv_heads"], z["dim"], z["streams"], 16, torch.bfloat16, "cuda"
+    dk, dv, G, J = 128, h // nh, nh // 2, 4
+    rows = []
+
+    def rnd(*shape, dtype=bf, scale=1.0):
+        return (torch.randn(*shape, device=dev) * scale).to(dtype)
+
+    def add(name, like, fn, copies, bytes_=0, flops=0, peak=None):
+        us = ops.time_in_graph(fn, reps=max(4, copies))
+        rate = bytes_ / us / 1e3 if bytes_ else flops / us / 1e6
+        row = {"kernel": name, "like": like, "us": round(us, 2), ("gb_s" if bytes_ else "tflop_s"): round(rate, 1)}
+        if bytes_ or peak != "none":
+            row["of_peak"] = round(rate / (peaks["hbm_gbs"] if bytes_ else peaks["bf16_tflops"]), 4)
+        rows.append(row)
+
+    ones = lambda n: torch.ones(n, device=dev)
+    # ---- rows of the residual streams
+    for t in (64, 2048):
+        c = 6 if t == 64 else 3
+        x = [rnd(S, t, h, dtype=torch.float32) for _ in range(c)]
+        y, o1 = ([rnd(t, h) for _ in range(c)] for _ in range(2))
+        mix, coef, gain, bias = torch.eye(S, device=dev), ones(S), ones(h), torch.zeros(h, device=dev)
+        add(f"{S} streams rejoined + next sublayer's read + layer norm, {t} tokens", "", lambda i: ops.stream_join(
+            x[i % c], y[i % c], mix, coef, 1e-6, next_coef=coef, next_w=gain, next_b=bias, next_out=o1[i % c]), c, bytes_=t * h * (8 * S + 4))
+        x1 = [rnd(t, h, dtype=torch.float32) for _ in range(c)]
+        add(f"Retodra: post norm + layer scale + addition + next norm, {t} tokens", "like the one above",
+            lambda i: ops.norm_residual_norm(y[i % c], gain, x1[i % c], 1e-6, next_gain=gain, next_out=o1[i % c], next_eps=1e-6), c, bytes_=t * h * 12)
+    # ---- the short convolutions and the recurrent unit: single tokens of a batch, then a prompt
+    for n_reqs, per in ((64, 1), (1, LUTODRA_PROMPT)):
+        t, c = n_reqs * per, 3
+        what = f"decode, batch {n_reqs}" if per == 1 else f"prompt of {per}"
+        q_start = torch.arange(0, t + 1, per, dtype=torch.int32, device=dev)
+        slots = torch.arange(n_reqs, dtype=torch.int32, device=dev)
+        xin = [rnd(t, 2 * h) for _ in range(c)]
+        u = [torch.empty(t, h, device=dev) for _ in range(c)]
+        state = torch.zeros(n_reqs, J, h, device=dev)
+        taps, lam = rnd(h, J, dtype=torch.float32), torch.full((h,), 0.5, device=dev)
+        add(f"causal convolution of {J} taps, {h} channels, {what}", "Retodra: token shift is the nearest (two rows mixed)",
+            lambda i: ops.causal_conv(xin[i % c][:, h:], taps, state[:, 1:], u[i % c], q_start, slots, n_reqs, per, pre_bias=lam, bias=lam), c,
+            bytes_=t * h * 6 + 2 * n_reqs * (J - 1) * h * 4)
+        bs = h // nh
+        wa, wi = rnd(nh, bs, bs, scale=bs ** -0.5), rnd(nh, bs, bs, scale=bs ** -0.5)
+        decay, drive = ([torch.empty(t, h, device=dev) for _ in range(c)] for _ in range(2))
+        kw = dict(flops=4.0 * t * h * bs, peak="none") if per > 1 else dict(bytes_=2 * nh * bs * bs * 2 + t * h * 12)
+        add(f"gates of the recurrent unit ({nh} blocks of {bs}, float FMA), {what}", "", lambda i: ops.gate_blocks(
+            u[i % c], wa, wi, lam, lam, lam, decay[i % c], drive[i % c], 8.0), c, **kw)
+        for k in range(c):
+            decay[k].uniform_(0.5, 1.0)
+        act = [torch.empty(t, h, dtype=bf, device=dev) for _ in range(c)]
+        add(f"linear recurrence + gelu branch, {h} channels, {what}", "", lambda i: ops.linear_recurrence(
+            decay[i % c], drive[i % c], xin[i % c][:, :h], lam, state[:, 0], act[i % c], q_start, slots, n_reqs, per), c,
+            bytes_=t * h * 12 + 2 * n_reqs * h * 4)
+    # ---- the gated delta rule beside Retodra's recurrence with a decay per channel (64 key channels there, 128 here)
+    for n_reqs, per in ((8, 1), (64, 1), (1, LUTODRA_PROMPT)):
+        t = n_reqs * per
+        what = f"decode, batch {n_reqs}" if per == 1 else f"prompt of {per}, token by token"
+        q_start = torch.arange(0, t + 1, per, dtype=torch.int32, device=dev)
+        slots = torch.arange(n_reqs, dtype=torch.int32, device=dev)
+        c = 3 if per == 1 else 1
+        state = [torch.zeros(n_reqs, nh, dk, dv, device=dev) for _ in range(c)]
+        q, k, v = rnd(t, G * dk, dtype=torch.float32), rnd(t, G * dk, dtype=torch.float32), rnd(t, nh * dv, dtype=torch.float32)
+        beta, pre, o = rnd(t, nh), rnd(t, nh * dk), torch.empty(t, nh * dv, device=dev)
+        a_log, dtb = torch.zeros(nh, device=dev), torch.zeros(nh * dk, device=dev)
+        kw = dict(bytes_=n_reqs * nh * dk * dv * 8) if per == 1 else dict(flops=8.0 * t * nh * dk * dv, peak="none")
+        work = torch.empty(t * ops.gated_delta_work_row(nh, G, dk), device=dev)
+        add(f"gated delta rule, {nh} heads of {dk} x {dv}, {what}", "", lambda i: ops.gated_delta_scan(
+            q, k, v, beta, pre, a_log, dtb, state[i % c], o, q_start, slots, n_reqs, num_heads=nh, num_qk_heads=G, q_scale=dk ** -0.5,
+            unit_eps=1e-6, max_q_len=per, work=work), max(2, c), **kw)
+        state2 = [torch.zeros(n_reqs, nh, 64, dv, device=dev) for _ in range(c)]
+        q2, k2, pre2, bias2 = rnd(t, nh * 64), rnd(t, nh * 64, scale=0.1), rnd(t, nh * 64), torch.zeros(nh * 64, device=dev)
+        v2 = rnd(t, nh * dv)
+        kw = dict(bytes_=n_reqs * nh * 64 * dv * 8) if per == 1 else dict(flops=4.0 * t * nh * 64 * dv, peak="none")
+        add(f"Retodra: recurrence (decay per channel), {nh} heads of 64 x {dv}, {what}", "like the one above", lambda i: ops.decayed_state_scan(
+            q2, k2, v2, state2[i % c], o, q_start, slots, n_reqs, num_heads=nh, decay_pre=pre2, decay_bias=bias2, tau=16.0, q_scale=0.125),
+            max(2, c), **kw)
+    for t in (64, 2048):
+        c = 3
+        of = [rnd(t, nh * dv, dtype=torch.float32) for _ in range(c)]
+        gt, gw, o1 = rnd(t, nh * dv), ones(dv), [torch.empty(t, nh * dv, dtype=bf, device=dev) for _ in range(c)]
+        add(f"norm per head + sigmoid gate, {t} tokens", "the same kernel as Retodra's (silu there)", lambda i: ops.gated_group_norm(
+            of[i % c], gt, gw, o1[i % c], group=dv, eps=1e-6, gate_act="sigmoid"), c, bytes_=t * nh * dv * 8)
+        # ---- q/k norm per head + partial rotation + cache write beside Retodra's norm + cache write
+        width = (nh + 2 * nkv) * d + nh
+        proj = [rnd(t, width) for _ in range(c)]
+        n_pages = t // page + 2
+        kvc = torch.zeros(n_pages, 2 * nkv * page * d, dtype=bf, device=dev)
+        bt = torch.arange(n_pages, dtype=torch.int32, device=dev).view(1, -1)
+        req, pos = torch.zeros(t, dtype=torch.int32, device=dev), torch.arange(t, dtype=torch.int32, device=dev)
+        q_out = torch.empty(t, nh * d, dtype=bf, device=dev)
+        inv_freq = torch.from_numpy(np.power(1e6, -np.arange(d // 4, dtype=np.float64) * 4 / d).astype(np.float32)).to(dev)
+        sizes = dict(num_heads=nh, num_kv_heads=nkv, head_dim=d, v_head_dim=d, row=d, page_size=page, eps=1e-6, write_kv=True)
+        g_head, g_q, g_k = ones(d), ones(nh * d), ones(nkv * d)
+        add(f"q/k norm per head + rotation of {d // 2} of {d} + cache write, {t} tokens", "", lambda i: ops.qk_head_rope_cache_write(
+            proj[i % c], 0, nh * d, (nh + nkv) * d, g_head, g_head, inv_freq, q_out, kvc, pos, req, bt, **sizes), c,
+            bytes_=t * (nh + 2 * nkv) * d * 4)
+        add(f"Retodra: q/k norm over the projection + cache write, {t} tokens", "like the one above", lambda i: ops.qk_norm_cache_write(
+            proj[i % c], 0, nh * d, (nh + nkv) * d, g_q, g_k, q_out, kvc, pos, req, bt, **sizes), c,
+            bytes_=t * (nh + 2 * nkv) * d * 4)
+    rows += lutodra_attention_kernels(z, peaks, add, rnd)
+    return rows
+
+
+def lutodra_attention_kernels(z, peaks, add, rnd):
+    """Attention with a sink and a gate per head beside plain attention (the same kernels without the epilogue), and the
+    routed experts with grouped sigmoid routing beside a dense gated feed-forward of the chosen experts' width."""
+    import numpy as np
+    import torch
+    from vllm_cpp_b200.config.model_spec import PartSpec
+    from vllm_cpp_b200.csrc import ops
+    from vllm_cpp_b200.engine.runner import HostStep
+    from vllm_cpp_b200.parts.attention import PagedAttention
+    from vllm_cpp_b200.parts.base import Workspace
+    from vllm_cpp_b200.parts.mlp import GatedMLP
+    from vllm_cpp_b200.parts.moe import RoutedExperts
+    h, nh, nkv, d, page, bf, dev = z["width"], z["heads"], z["kv_heads"], z["dim"], 16, torch.bfloat16, "cuda"
+    t = LUTODRA_PROMPT
+    n_pages = t // page + 2
+    bt = torch.arange(n_pages, dtype=torch.int32, device=dev).view(1, -1)
+    q_start, ctx = torch.tensor([0, t], dtype=torch.int32, device=dev), torch.zeros(1, dtype=torch.int32, device=dev)
+    G = nh // nkv
+    n_tiles = -(-t * G // ops.TC_ATTENTION_TILE_ROWS)
+    tile_req = torch.zeros(n_tiles, dtype=torch.int32, device=dev)
+    tile_row0 = torch.from_numpy((np.arange(n_tiles, dtype=np.int32) * ops.TC_ATTENTION_TILE_ROWS)[::-1].copy()).to(dev)
+    q, o = rnd(t, nh * d), torch.empty(t, nh * d, dtype=bf, device=dev)
+    kv = rnd(n_pages, 2, nkv, page * d, scale=0.5)
+    sink, gate = rnd(nh, dtype=torch.float32), rnd(t, nh)
+    seen = t * (t + 1) // 2
+    for epi, name, like in ((True, f"attention with sink and head gate, prompt of {t}", ""),
+                            (False, f"Qwen2: attention, prompt of {t}", "like the one above")):
+        kw = dict(sink=sink, head_gate=gate) if epi else {}
+        add(name, like, lambda i: ops.attention_prefill_tc(q, kv, o, q_start, ctx, bt, tile_req, tile_row0, num_heads=nh, num_kv_heads=nkv, head_dim=d,
+                                                           page_size=page, window=0, scale=d ** -0.5, **kw), 4, flops=4.0 * nh * d * seen)
+    part = PagedAttention(h, nh, nkv, d, True, False, 0, PartSpec("none"), bf, dev)
+    for batch in (8, 64):
+        contexts = [LUTODRA_CONTEXT - 1] * batch
+        blocks = -(-LUTODRA_CONTEXT // page)
+        bt = torch.arange(batch * blocks, dtype=torch.int32, device=dev).view(batch, blocks)
+        q_start, ctx = torch.arange(batch + 1, dtype=torch.int32, device=dev), torch.tensor(contexts, dtype=torch.int32, device=dev)
+        host = HostStep([1] * batch, contexts, page)
+        split_tiles = torch.from_numpy(part.step_arrays()[part._splits_key()](host)).to(dev)
+        nsplit = host.shapes[part._splits_key()]
+        need = batch * nh * nsplit
+        share = ops.decode_head_groups(nh, nkv)
+        po, pml, tickets = torch.empty(need * d, device=dev), torch.empty(need * 2, device=dev), torch.zeros(batch * nkv * share, dtype=torch.int32, device=dev)
+        q, o = rnd(batch, nh * d), torch.empty(batch, nh * d, dtype=bf, device=dev)
+        kv = rnd(batch * blocks + 1, 2, nkv, page * d, scale=0.5)
+        gate = rnd(batch, nh)
+        for epi, name, like in ((True, f"attention with sink and head gate, decode, batch {batch}, context {LUTODRA_CONTEXT}", ""),
+                                (False, f"Qwen2: attention, decode, batch {batch}, context {LUTODRA_CONTEXT}", "like the one above")):
+            kw = dict(sink=sink, head_gate=gate) if epi else {}
+            add(name, like, lambda i: ops.attention_decode_mma(q, kv, o, q_start, ctx, bt, None, batch, nsplit, po, pml, tickets, num_heads=nh,
+                                                               num_kv_heads=nkv * share, head_dim=d, page_size=page, window=0, scale=d ** -0.5,
+                                                               split_tiles=split_tiles, kv_share=share, **kw), 4,
+                bytes_=batch * LUTODRA_CONTEXT * 2 * nkv * d * 2)
+    # ---- routed experts (sigmoid scores, groups) beside a dense gated feed-forward of the width the chosen experts have together
+    E, top, ff = z["experts"], z["top"], z["expert_ff"]
+    moe = RoutedExperts(h, ff, E, 0, top, float("inf"), bf, dev, activation="silu", score="sigmoid", correction=False, groups=4, keep_groups=2,
+                        group_top=2, normalize=True, sum_eps=1e-20, route_scale=2.5)
+    tensors = {"router": rnd(E, h, dtype=torch.float32, scale=0.05)}
+    for e in range(E):
+        tensors.update({f"e{e}.gate": rnd(ff, h, scale=0.02), f"e{e}.up": rnd(ff, h, scale=0.02), f"e{e}.down": rnd(h, ff, scale=0.02)})
+    moe.load_params(tensors)
+    del tensors
+    dense = [GatedMLP(h, top * ff, "silu", bf, dev) for _ in range(3)]
+    for m in dense:
+        m.load_params({"gate_proj.weight": rnd(top * ff, h, scale=0.02), "up_proj.weight": rnd(top * ff, h, scale=0.02),
+                       "down_proj.weight": rnd(h, top * ff, scale=0.02)})
+        ops.tile_weights(m.w_gate_up, top * ff)
+        ops.tile_weights(m.w_down)
+    ws = Workspace(dev, 1 << 30)
+    for t in (8, 64, 2048):
+        x, out = rnd(t, h), torch.empty(t, h, dtype=bf, device=dev)
+
+        def run_moe(i):
+            ws.reset()
+            moe.forward(x, out, None, ws)
+
+        def run_dense(i):
+            ws.reset()
+            dense[i % 3].forward(x, out, None, ws)
+
+        reach = min(E, t * top)
+        kw = dict(bytes_=reach * 3 * ff * h * 2) if t <= 128 else dict(flops=6.0 * t * top * ff * h)
+        add(f"routed experts ({top} of {E} in 4 groups of which 2 stay), {t} tokens", "", run_moe, 3, **kw)
+        kw = dict(bytes_=3 * top * ff * h * 2) if t <= 128 else dict(flops=6.0 * t * top * ff * h)
+        add(f"Qwen2: gated feed-forward of width {top * ff}, {t} tokens", "like the one above", run_dense, 3, **kw)
+    ops.check_status()
+    return []
+
+
 # ------------------------------------------------------------------------------------------ reference arm
 REFERENCE_NOTES = ("the reference's own faults at these sizes, none of which changes the work of a step: an untied lm_head is "
                    "copied over the embedding table (src/model/qwen.cpp:279-281); the bias area of 3*1024 floats a layer "
@@ -1138,6 +1390,9 @@ def main() -> int:
                     help="instead of the benchmark's workload: prefill and decode throughput of the Rolesun design beside Qwen2 "
                          f"at equal layer sizes ({','.join(sorted(ROLESUN_SIZES))} or 'all'), and the design's kernels alone "
                          "beside the like kernels of Qwen2's layer")
+    ap.add_argument("--lutodra", default="", metavar="SIZES",
+                    help="instead of the benchmark's workload: prefill and decode throughput of the Lutodra design beside Retodra "
+                         "at equal layer sizes, and the design's kernels alone: 'all' or a comma list of " + ",".join(sorted(LUTODRA_SIZES)))
     ap.add_argument("--retodra", default="", metavar="SIZES",
                     help="instead of the benchmark's workload: prefill and decode throughput of the Retodra design beside Qwen2 "
                          f"at equal layer sizes ({','.join(sorted(RETODRA_SIZES))} or 'all'), and the design's kernels alone "
@@ -1177,6 +1432,8 @@ def main() -> int:
         return run_rolesun(a)
     if a.retodra:
         return run_retodra(a)
+    if a.lutodra:
+        return run_lutodra(a)
     if a.mix:
         return run_mix(cfg, a)
     if a.kernels:

@@ -351,7 +351,7 @@ def test_a_key_written_long_before_it_is_asked_for(H, G, dk, dv, planted_at, cut
         ops.gated_delta_scan(pack(q, "q"), pack(k, "k"), pack(v, "v"), pack(beta_pre, "b"), pack(decay_pre, "d"), dev(np.float32(a_log)),
                              dev(np.float32(dt_bias).reshape(-1)), state, out, dev(np.array([0, 1, s + 1], dtype=np.int32)),
                              dev(np.array([2, 1], dtype=np.int32)), 2, num_heads=H, num_qk_heads=G, q_scale=dk ** -0.5,
-                             unit_eps=plain.UNIT_EPS)
+                             unit_eps=plain.UNIT_EPS, max_q_len=s)
         got[t: t + s] = out[1:].cpu().numpy().reshape(s, H, dv)
         t += s
     ops.check_status()

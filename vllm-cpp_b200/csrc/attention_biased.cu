@@ -236,6 +236,17 @@ __global__ void qk_head_rope_cache_write_kernel(QkHeadArgs h) {
             vp = kp + (size_t)a.G * block;
         }
     }
+    // the angles depend on the position and the pair only: a lane keeps cosine and sine of its pairs for all the heads
+    // its warp takes (pairs lane, lane + 32, ...; beyond ROPE_KEPT * 32 pairs they are made where they are used)
+    constexpr int ROPE_KEPT = 4;
+    float cs[ROPE_KEPT], sn[ROPE_KEPT];
+#pragma unroll
+    for (int k = 0; k < ROPE_KEPT; ++k) {
+        const int j = lane + 32 * k;
+        cs[k] = 1.0f;
+        sn[k] = 0.0f;
+        if (j < half) sincosf((float)pos * h.inv_freq[j], &sn[k], &cs[k]);
+    }
     for (int head = warp; head < a.H + a.G; head += nwarps) {
         const bool is_q = head < a.H;
         const int g = is_q ? head : head - a.H;
@@ -250,18 +261,28 @@ __global__ void qk_head_rope_cache_write_kernel(QkHeadArgs h) {
         if (!is_q && !kp) continue;
         T* qo = (T*)a.q_out + (size_t)t * a.H * a.dk + (size_t)g * a.dk;
         T* ko = is_q ? nullptr : kp + (size_t)g * block;
-        for (int i = lane; i < a.dk; i += 32) {
-            float v = to_f32<T>(x[i]) * r * (w ? w[i] : 1.0f);
-            if (i < h.rot) {
-                const int j = i < half ? i : i - half, partner = i < half ? i + half : i - half;
-                const float pv = to_f32<T>(x[partner]) * r * (w ? w[partner] : 1.0f);
-                float sn, cs;
-                sincosf((float)pos * h.inv_freq[j], &sn, &cs);
-                v = i < half ? v * cs - pv * sn : v * cs + pv * sn;
-            }
+        auto put = [&](int i, float v) {
             if (is_q) qo[i] = from_f32<T>(v);
             else ko[kv_pos(i, slot, a.row, a.page, (int)sizeof(T))] = from_f32<T>(v);
+        };
+        // a pair (j, j + half) at a time, then the coordinates that no rotation turns
+#pragma unroll
+        for (int k = 0; k < ROPE_KEPT; ++k) {
+            const int j = lane + 32 * k;
+            if (j < half) {
+                const float u = to_f32<T>(x[j]) * r * (w ? w[j] : 1.0f), v = to_f32<T>(x[j + half]) * r * (w ? w[j + half] : 1.0f);
+                put(j, u * cs[k] - v * sn[k]);
+                put(j + half, v * cs[k] + u * sn[k]);
+            }
         }
+        for (int j = lane + 32 * ROPE_KEPT; j < half; j += 32) {
+            float s1, c1;
+            sincosf((float)pos * h.inv_freq[j], &s1, &c1);
+            const float u = to_f32<T>(x[j]) * r * (w ? w[j] : 1.0f), v = to_f32<T>(x[j + half]) * r * (w ? w[j + half] : 1.0f);
+            put(j, u * c1 - v * s1);
+            put(j + half, v * c1 + u * s1);
+        }
+        for (int i = h.rot + lane; i < a.dk; i += 32) put(i, to_f32<T>(x[i]) * r * (w ? w[i] : 1.0f));
     }
     if (!vp) return;
     const int nv = a.G * a.dv;

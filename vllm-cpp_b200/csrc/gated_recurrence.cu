@@ -242,13 +242,99 @@ linear_recurrence_kernel(const float* __restrict__ decay, const float* __restric
     *st = S;
 }
 
+// The same for portions of many tokens: a CTA owns 32 channels (the lanes) of a request, its SCAN_WARPS warps a
+// stretch of the portion each.  Every warp first walks its stretch from an empty state and keeps the stretch's total decay
+// A and its own contribution B (S_end = A S_start + B); one warp then carries the request's state through the stretches
+// in order; then every warp walks its stretch again from the state it starts with and writes the outputs.  Within a
+// stretch the recurrence runs token by token as above; only the states at the stretches' starts are summed in another
+// order.
+constexpr int SCAN_WARPS = 32, SCAN_AHEAD = 8;
+template <typename T>
+__global__ void __launch_bounds__(SCAN_WARPS * 32)
+linear_recurrence_stretches_kernel(const float* __restrict__ decay, const float* __restrict__ drive, long long ldd,
+                                   const T* __restrict__ y, long long ldy, const float* __restrict__ by, float* __restrict__ state,
+                                   long long slot_stride, T* __restrict__ out, long long ldo, const int* __restrict__ q_start,
+                                   const int* __restrict__ state_slots, int W) {
+    __shared__ float As[SCAN_WARPS][32], Bs[SCAN_WARPS][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int c = blockIdx.y * 32 + lane;
+    const bool ok = c < W;
+    const float yb = (ok && by) ? by[c] : 0.0f;
+    pdl_start();
+    const int r = blockIdx.x;
+    const int row0 = q_start[r], len = q_start[r + 1] - row0;
+    const int per = (len + SCAN_WARPS - 1) / SCAN_WARPS;
+    const int t0 = row0 + min(warp * per, len), t1 = row0 + min((warp + 1) * per, len);
+    float A = 1.0f, B = 0.0f;
+    if (ok) {
+        int t = t0;
+        for (; t + SCAN_AHEAD <= t1; t += SCAN_AHEAD) {
+            float a[SCAN_AHEAD], b[SCAN_AHEAD];
+#pragma unroll
+            for (int k = 0; k < SCAN_AHEAD; ++k) { a[k] = decay[(size_t)(t + k) * ldd + c]; b[k] = drive[(size_t)(t + k) * ldd + c]; }
+#pragma unroll
+            for (int k = 0; k < SCAN_AHEAD; ++k) { B = fmaf(a[k], B, b[k]); A *= a[k]; }
+        }
+        for (; t < t1; ++t) { const float a = decay[(size_t)t * ldd + c]; B = fmaf(a, B, drive[(size_t)t * ldd + c]); A *= a; }
+    }
+    As[warp][lane] = A;
+    Bs[warp][lane] = B;
+    __syncthreads();
+    if (warp == 0 && ok) {
+        float* st = state + (size_t)state_slots[r] * slot_stride + c;
+        float S = *st;
+        for (int w = 0; w < SCAN_WARPS; ++w) {
+            const float a = As[w][lane], b = Bs[w][lane];
+            As[w][lane] = S;                              // the state the stretch starts with
+            S = fmaf(a, S, b);
+        }
+        *st = S;
+    }
+    __syncthreads();
+    if (!ok) return;
+    float S = As[warp][lane];
+    int t = t0;
+    for (; t + SCAN_AHEAD <= t1; t += SCAN_AHEAD) {
+        float a[SCAN_AHEAD], b[SCAN_AHEAD], g[SCAN_AHEAD];
+#pragma unroll
+        for (int k = 0; k < SCAN_AHEAD; ++k) {
+            a[k] = decay[(size_t)(t + k) * ldd + c];
+            b[k] = drive[(size_t)(t + k) * ldd + c];
+            g[k] = to_f32<T>(y[(size_t)(t + k) * ldy + c]);
+        }
+#pragma unroll
+        for (int k = 0; k < SCAN_AHEAD; ++k) {
+            S = fmaf(a[k], S, b[k]);
+            out[(size_t)(t + k) * ldo + c] = from_f32<T>(S * gr_gelu_tanh(g[k] + yb));
+        }
+    }
+    for (; t < t1; ++t) {
+        S = fmaf(decay[(size_t)t * ldd + c], S, drive[(size_t)t * ldd + c]);
+        out[(size_t)t * ldo + c] = from_f32<T>(S * gr_gelu_tanh(to_f32<T>(y[(size_t)t * ldy + c]) + yb));
+    }
+}
+
+constexpr int SCAN_STRETCHES_FROM = 64;      // portions of at least this many tokens in a step: the kernel above
+
 VCB_EXPORT int vcb_linear_recurrence(const float* decay, const float* drive, long long ldd, const void* y, long long ldy,
                                      const float* by, float* state, long long slot_stride, void* out, long long ldo,
-                                     const int* q_start, const int* state_slots, int n_reqs, int W, int dtype, void* stream) {
+                                     const int* q_start, const int* state_slots, int n_reqs, int max_q_len, int W, int dtype,
+                                     void* stream) {
     if (n_reqs <= 0) return 0;
-    if (!decay || !drive || !y || !state || !out || W <= 0 || (W + 127) / 128 > 65535) return VCB_ERR_BAD_ARG;
-    dim3 grid(n_reqs, (W + 127) / 128);
+    if (!decay || !drive || !y || !state || !out || W <= 0 || (W + 31) / 32 > 65535) return VCB_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
+    if (max_q_len >= SCAN_STRETCHES_FROM) {
+        dim3 grid(n_reqs, (W + 31) / 32);
+        if (dtype == VCB_F32)
+            vcb_launch(linear_recurrence_stretches_kernel<float>, grid, SCAN_WARPS * 32, 0, s, decay, drive, ldd, (const float*)y, ldy, by,
+                       state, slot_stride, (float*)out, ldo, q_start, state_slots, W);
+        else if (dtype == VCB_BF16)
+            vcb_launch(linear_recurrence_stretches_kernel<__nv_bfloat16>, grid, SCAN_WARPS * 32, 0, s, decay, drive, ldd,
+                       (const __nv_bfloat16*)y, ldy, by, state, slot_stride, (__nv_bfloat16*)out, ldo, q_start, state_slots, W);
+        else return VCB_ERR_BAD_ARG;
+        return vcb_last_error();
+    }
+    dim3 grid(n_reqs, (W + 127) / 128);
     if (dtype == VCB_F32)
         vcb_launch(linear_recurrence_kernel<float>, grid, 128, 0, s, decay, drive, ldd, (const float*)y, ldy, by, state, slot_stride,
                    (float*)out, ldo, q_start, state_slots, W);
@@ -397,6 +483,238 @@ __global__ void gated_delta_scan_kernel(DeltaArgs a, int P, int DVT) {
     }
 }
 
+// ---- the same for steps that bring portions of many tokens, in two kernels.
+// delta_prepare_kernel, a warp per token and head: what the recurrence reads per token, into rows of float
+//   work[t] = [ q: G * dk | k: G * dk | g: H * dk | beta: H | qk: G ]   (q, k unit vectors, q scaled; qk = q . k)
+// so that nothing but the recurrence itself is left in the walk over the tokens.
+template <typename T>
+__global__ void __launch_bounds__(128)
+delta_prepare_kernel(DeltaArgs a, float* __restrict__ work, long long ldw, int n) {
+    pdl_start();
+    const int lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (item >= (long long)n * a.H) return;
+    const size_t row = (size_t)(item / a.H);
+    const int h = (int)(item % a.H);
+    float* w = work + row * ldw;
+    const int per = a.H / a.G, dk = a.dk;
+    if (h % per == 0) {                                   // the first head of a group norms the group's q and k
+        const int kvh = h / per;
+        const float* qr = a.q + row * a.ldq + kvh * dk;
+        const float* kr = a.k + row * a.ldk + kvh * dk;
+        float sq = 0.0f, sk = 0.0f, qk = 0.0f;
+        for (int i = lane; i < dk; i += 32) { const float x = qr[i], y = kr[i]; sq = fmaf(x, x, sq); sk = fmaf(y, y, sk); qk = fmaf(x, y, qk); }
+        sq = warp_sum(sq);
+        sk = warp_sum(sk);
+        qk = warp_sum(qk);
+        const float rq = a.q_scale / sqrtf(sq + a.unit_eps), rk = 1.0f / sqrtf(sk + a.unit_eps);
+        for (int i = lane; i < dk; i += 32) { w[kvh * dk + i] = qr[i] * rq; w[(a.G + kvh) * dk + i] = kr[i] * rk; }
+        if (lane == 0) w[(2 * a.G + a.H) * dk + a.H + kvh] = qk * rq * rk;
+    }
+    const float rate = expf(a.a_log[h]);
+    const T* dp = (const T*)a.decay_pre + row * a.lda + h * dk;
+    for (int i = lane; i < dk; i += 32)
+        w[(2 * a.G + h) * dk + i] = expf(-rate * gr_softplus(to_f32<T>(dp[i]) + a.dt_bias[h * dk + i]));
+    if (lane == 0) w[(2 * a.G + a.H) * dk + h] = gr_sigmoid(to_f32<T>(((const T*)a.beta_pre)[row * a.ldb + h]));
+}
+
+// delta_walk_kernel, grid (request, head, tile of DVT value channels), P lanes of a warp per column of S, DKP rows of
+// the column in a thread's registers.  With S' = diag(g) S, both sums over key channels that a token needs come from S':
+//   p = k . S'[:, c],  r = q . S'[:, c];   u = beta (v_c - p);   S[:, c] = S'[:, c] + k u;   o_c = r + (q . k) u
+// so a token costs one round of shuffles, for two sums at once.  Chunks of a.chunk tokens' rows go through shared memory.
+__device__ __forceinline__ void walk_copy(float* smem, const float* gmem, int bytes) {
+    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem);
+    if (bytes == 16) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gmem) : "memory");
+    else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(gmem) : "memory");
+}
+
+template <int DKP>
+__global__ void __launch_bounds__(128)
+delta_walk_kernel(DeltaArgs a, const float* __restrict__ work, long long ldw, int P, int DVT) {
+    extern __shared__ __align__(16) float sm[];
+    pdl_start();
+    const int r = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * DVT;
+    const int kvh = h / (a.H / a.G);
+    const int tid = threadIdx.x, nthreads = blockDim.x;
+    const int part = tid % P, cl = tid / P;
+    const int col = col0 + cl;
+    const bool col_ok = cl < DVT && col < a.dv;
+    const int pstride = DKP + 4, tstride = P * pstride, dk = a.dk, TC = a.chunk;
+    // two buffers of a chunk's rows, filled by asynchronous copies while the chunk before is walked:
+    // [q, k, g: TC x tstride each][v: TC x DVT][beta, q . k: TC x 2], then the chunk's outputs [TC x DVT]
+    const int buf_floats = TC * (3 * tstride + DVT + 2);
+    float* os = sm + 2 * buf_floats;
+    const int row0 = a.q_start[r], row1 = a.q_start[r + 1];
+    float* st = a.state + (((size_t)a.state_slots[r] * a.H + h) * dk) * a.dv;
+    float S[DKP];
+#pragma unroll
+    for (int i = 0; i < DKP; ++i) {
+        const int kr = part * DKP + i;
+        S[i] = (col_ok && kr < dk) ? st[(size_t)kr * a.dv + col] : 0.0f;
+    }
+    const int off_q = kvh * dk, off_k = (a.G + kvh) * dk, off_g = (2 * a.G + h) * dk, off_b = (2 * a.G + a.H) * dk;
+    // key channels beyond dk: q = k = 0, g = 1, written once (the copies never touch them)
+    for (int idx = tid; idx < 2 * TC * P * DKP; idx += nthreads) {
+        const int b = idx / (TC * P * DKP), rest = idx - b * (TC * P * DKP);
+        const int tt = rest / (P * DKP), i = rest - tt * (P * DKP);
+        if (i >= dk) {
+            float* base = sm + b * buf_floats + tt * tstride + (i / DKP) * pstride + i % DKP;
+            base[0] = 0.0f;
+            base[TC * tstride] = 0.0f;
+            base[2 * TC * tstride] = 1.0f;
+        }
+    }
+    const bool wide = (dk & 3) == 0;               // rows of the prepared inputs start on 16 bytes, so do their heads then
+    const int piece = wide ? 4 : 1, pieces = dk / piece;
+    auto fetch = [&](int c0, int b) {
+        const int tc = min(TC, row1 - c0);
+        float* qs = sm + b * buf_floats;
+        float* vs = qs + 3 * TC * tstride;
+        float* bs = vs + TC * DVT;
+        for (int idx = tid; idx < tc * pieces; idx += nthreads) {
+            const int tt = idx / pieces, i = (idx - tt * pieces) * piece;
+            const float* w = work + (size_t)(c0 + tt) * ldw;
+            float* at = qs + tt * tstride + (i / DKP) * pstride + i % DKP;
+            walk_copy(at, w + off_q + i, 4 * piece);
+            walk_copy(at + TC * tstride, w + off_k + i, 4 * piece);
+            walk_copy(at + 2 * TC * tstride, w + off_g + i, 4 * piece);
+        }
+        for (int idx = tid; idx < tc * DVT; idx += nthreads) {
+            const int tt = idx / DVT, j = idx - tt * DVT, c = col0 + j;
+            if (c < a.dv) walk_copy(vs + idx, a.v + (size_t)(c0 + tt) * a.ldv + h * a.dv + c, 4);
+        }
+        for (int idx = tid; idx < 2 * tc; idx += nthreads) {
+            const int tt = idx >> 1;
+            walk_copy(bs + idx, work + (size_t)(c0 + tt) * ldw + off_b + ((idx & 1) ? a.H + kvh : h), 4);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (row0 < row1) fetch(row0, 0);
+    int b = 0;
+    for (int c0 = row0; c0 < row1; c0 += TC, b ^= 1) {
+        const int tc = min(TC, row1 - c0);
+        if (c0 + TC < row1) {
+            fetch(c0 + TC, b ^ 1);                 // its buffer was walked two chunks ago; the barriers since cover it
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();                           // everybody's copies of this chunk have landed; the outputs before are stored
+        const float* qs = sm + b * buf_floats;
+        const float* ks = qs + TC * tstride;
+        const float* gs = ks + TC * tstride;
+        const float* vs = gs + TC * tstride;
+        const float* bs = vs + TC * DVT;
+        if (cl < DVT) {
+            // the rows of the token after this one are read from shared memory while this one's sums run
+            float4 q4[DKP / 4], k4[DKP / 4], g4[DKP / 4], qn[DKP / 4], kn[DKP / 4], gn[DKP / 4];
+            const float* mine = qs + part * pstride;
+#pragma unroll
+            for (int i = 0; i < DKP / 4; ++i) {
+                qn[i] = reinterpret_cast<const float4*>(mine)[i];
+                kn[i] = reinterpret_cast<const float4*>(mine + TC * tstride)[i];
+                gn[i] = reinterpret_cast<const float4*>(mine + 2 * TC * tstride)[i];
+            }
+            float beta_n = bs[0], qk_n = bs[1], v_n = col_ok ? vs[cl] : 0.0f;
+            for (int tt = 0; tt < tc; ++tt) {
+#pragma unroll
+                for (int i = 0; i < DKP / 4; ++i) { q4[i] = qn[i]; k4[i] = kn[i]; g4[i] = gn[i]; }
+                const float beta = beta_n, qk = qk_n, vv = v_n;
+                if (tt + 1 < tc) {
+                    const float* next = mine + (tt + 1) * tstride;
+#pragma unroll
+                    for (int i = 0; i < DKP / 4; ++i) {
+                        qn[i] = reinterpret_cast<const float4*>(next)[i];
+                        kn[i] = reinterpret_cast<const float4*>(next + TC * tstride)[i];
+                        gn[i] = reinterpret_cast<const float4*>(next + 2 * TC * tstride)[i];
+                    }
+                    beta_n = bs[2 * tt + 2];
+                    qk_n = bs[2 * tt + 3];
+                    v_n = col_ok ? vs[(tt + 1) * DVT + cl] : 0.0f;
+                }
+                float p0 = 0.0f, p1 = 0.0f, p2 = 0.0f, p3 = 0.0f, r0 = 0.0f, r1 = 0.0f, r2 = 0.0f, r3 = 0.0f;
+#pragma unroll
+                for (int i = 0; i < DKP / 4; ++i) {
+                    S[4 * i] *= g4[i].x; S[4 * i + 1] *= g4[i].y; S[4 * i + 2] *= g4[i].z; S[4 * i + 3] *= g4[i].w;
+                    p0 = fmaf(S[4 * i], k4[i].x, p0);     r0 = fmaf(S[4 * i], q4[i].x, r0);
+                    p1 = fmaf(S[4 * i + 1], k4[i].y, p1); r1 = fmaf(S[4 * i + 1], q4[i].y, r1);
+                    p2 = fmaf(S[4 * i + 2], k4[i].z, p2); r2 = fmaf(S[4 * i + 2], q4[i].z, r2);
+                    p3 = fmaf(S[4 * i + 3], k4[i].w, p3); r3 = fmaf(S[4 * i + 3], q4[i].w, r3);
+                }
+                float p = (p0 + p1) + (p2 + p3), rr = (r0 + r1) + (r2 + r3);
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    if (o < P) {
+                        p += __shfl_xor_sync(0xffffffffu, p, o);
+                        rr += __shfl_xor_sync(0xffffffffu, rr, o);
+                    }
+                }
+                const float u = beta * (vv - p);
+#pragma unroll
+                for (int i = 0; i < DKP / 4; ++i) {
+                    S[4 * i] = fmaf(k4[i].x, u, S[4 * i]);
+                    S[4 * i + 1] = fmaf(k4[i].y, u, S[4 * i + 1]);
+                    S[4 * i + 2] = fmaf(k4[i].z, u, S[4 * i + 2]);
+                    S[4 * i + 3] = fmaf(k4[i].w, u, S[4 * i + 3]);
+                }
+                if (part == 0) os[tt * DVT + cl] = fmaf(qk, u, rr);
+            }
+        }
+        __syncthreads();
+        for (int idx = tid; idx < tc * DVT; idx += nthreads) {
+            const int tt = idx / DVT, j = idx - tt * DVT, c = col0 + j;
+            if (c < a.dv) a.out[(size_t)(c0 + tt) * a.ldo + h * a.dv + c] = os[idx];
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < DKP; ++i) {
+        const int kr = part * DKP + i;
+        if (col_ok && kr < dk) st[(size_t)kr * a.dv + col] = S[i];
+    }
+}
+
+// Floats of a token's row of the prepared inputs (ops.py has the same formula).
+static long long delta_work_row(int H, int G, int dk) { return ((long long)(2 * G + H) * dk + H + G + 3) / 4 * 4; }
+
+template <typename T>
+static int launch_delta(const DeltaArgs& a, int n_reqs, cudaStream_t s);
+
+constexpr int WALK_SMEM = 64 * 1024;
+
+template <int DKP>
+static int launch_walk(const DeltaArgs& b, dim3 grid, int threads, size_t bytes, const float* work, long long ldw, int P, int dvt,
+                       cudaStream_t s) {
+    static unsigned long long configured = 0;
+    if (int e = vcb_allow_dynamic_smem(delta_walk_kernel<DKP>, WALK_SMEM, &configured)) return e;
+    vcb_launch(delta_walk_kernel<DKP>, grid, threads, bytes, s, b, work, ldw, P, dvt);
+    return vcb_last_error();
+}
+
+template <typename T>
+static int launch_delta_portions(const DeltaArgs& a, int n_reqs, int n_tokens, float* work, cudaStream_t s) {
+    // 8 rows of a column per thread where the key channels fill 16 lanes (keys of 128), fewer lanes for shorter keys, 16 rows
+    // for longer ones; CTAs of four warps, so that a head's columns spread over many SMs.  Measured at 16 heads of 128 x 128
+    // over 2,048 tokens: 16 rows a thread or 4 rows in CTAs of 16 warps are both slower.
+    const int dkp = a.dk > 256 ? 16 : 8;
+    int P = 1;
+    while (P * dkp < a.dk) P <<= 1;
+    const int dvt = 128 / P >= 32 ? 32 : 128 / P;
+    int chunk = 16;
+    auto bytes = [&](int tc) { return (size_t)tc * (2 * (3 * P * (dkp + 4) + dvt + 2) + dvt) * sizeof(float); };
+    while (chunk > 4 && bytes(chunk) > WALK_SMEM) chunk >>= 1;
+    if (P > 32 || bytes(chunk) > WALK_SMEM) return launch_delta<T>(a, n_reqs, s);      // keys beyond 512 channels: the kernel above
+    const long long ldw = delta_work_row(a.H, a.G, a.dk);
+    const long long items = (long long)n_tokens * a.H;
+    vcb_launch(delta_prepare_kernel<T>, dim3((unsigned)((items + 3) / 4)), 128, 0, s, a, work, ldw, n_tokens);
+    if (int e = vcb_last_error()) return e;
+    DeltaArgs b = a;
+    b.chunk = chunk;
+    dim3 grid(n_reqs, a.H, (a.dv + dvt - 1) / dvt);
+    const int threads = dvt * P;
+    if (dkp == 8) return launch_walk<8>(b, grid, threads, bytes(chunk), work, ldw, P, dvt, s);
+    return launch_walk<16>(b, grid, threads, bytes(chunk), work, ldw, P, dvt, s);
+}
+
 template <typename T>
 static int launch_delta(const DeltaArgs& a, int n_reqs, cudaStream_t s) {
     const int dkp = a.dk <= 32 ? 8 : a.dk <= 64 ? 16 : 32;
@@ -421,7 +739,7 @@ VCB_EXPORT int vcb_gated_delta_scan(const float* q, const float* k, const float*
                                     const void* beta_pre, long long ldb, const void* decay_pre, long long lda,
                                     const float* a_log, const float* dt_bias, float* state, float* out, long long ldo,
                                     const int* q_start, const int* state_slots, int n_reqs, int H, int G, int dk, int dv,
-                                    float q_scale, float unit_eps, int dtype, void* stream) {
+                                    float q_scale, float unit_eps, int dtype, float* work, int n_tokens, void* stream) {
     if (n_reqs <= 0) return 0;
     if (!q || !k || !v || !beta_pre || !decay_pre || !a_log || !dt_bias || !state || !out || H <= 0 || G <= 0 || H % G ||
         dk <= 0 || dv <= 0 || H > 65535 || (dv + 7) / 8 > 65535)
@@ -429,6 +747,11 @@ VCB_EXPORT int vcb_gated_delta_scan(const float* q, const float* k, const float*
     DeltaArgs a{q, k, v, ldq, ldk, ldv, beta_pre, ldb, decay_pre, lda, a_log, dt_bias, state, out, ldo, q_start, state_slots,
                 H, G, dk, dv, q_scale, unit_eps, 0};
     cudaStream_t s = (cudaStream_t)stream;
+    if (work && n_tokens > 0) {                   // a step with portions: inputs prepared for all tokens at once, then the walk
+        if (dtype == VCB_F32) return launch_delta_portions<float>(a, n_reqs, n_tokens, work, s);
+        if (dtype == VCB_BF16) return launch_delta_portions<__nv_bfloat16>(a, n_reqs, n_tokens, work, s);
+        return VCB_ERR_BAD_ARG;
+    }
     if (dtype == VCB_F32) return launch_delta<float>(a, n_reqs, s);
     if (dtype == VCB_BF16) return launch_delta<__nv_bfloat16>(a, n_reqs, s);
     return VCB_ERR_BAD_ARG;

@@ -72,8 +72,8 @@ _SIGNATURES = {
     "vcb_stream_join": [_P, _L, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _I, _P],
     "vcb_causal_conv": [_P, _L, _P, _P, _P, _P, _L, _P, _L, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "vcb_gate_blocks": [_P, _L, _P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _F, _I, _P],
-    "vcb_linear_recurrence": [_P, _P, _L, _P, _L, _P, _P, _L, _P, _L, _P, _P, _I, _I, _I, _P],
-    "vcb_gated_delta_scan": [_P, _P, _P, _L, _L, _L, _P, _L, _P, _L, _P, _P, _P, _P, _L, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _P],
+    "vcb_linear_recurrence": [_P, _P, _L, _P, _L, _P, _P, _L, _P, _L, _P, _P, _I, _I, _I, _I, _P],
+    "vcb_gated_delta_scan": [_P, _P, _P, _L, _L, _L, _P, _L, _P, _L, _P, _P, _P, _P, _L, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _P, _I, _P],
     "vcb_moe_sort": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P],
     "vcb_moe_expert_gemm": [_P, _L, _P, _P, _L, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _F, _F, _F, _I, _P],
     "vcb_moe_combine": [_P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _P],
@@ -1267,9 +1267,10 @@ def gate_blocks(u: torch.Tensor, wa: torch.Tensor, wi: torch.Tensor, ba: torch.T
 
 
 def linear_recurrence(decay: torch.Tensor, drive: torch.Tensor, y: torch.Tensor, y_bias: Optional[torch.Tensor],
-                      state: torch.Tensor, out: torch.Tensor, q_start, state_slots, n_reqs: int) -> None:
+                      state: torch.Tensor, out: torch.Tensor, q_start, state_slots, n_reqs: int, max_q_len: int = 1) -> None:
     """S_t = decay_t * S_(t-1) + drive_t per channel and request, S read from and left in the request's slot of ``state``
-    (float32 [slots, W] as a strided view); out = S_t * gelu_tanh(y_t + y_bias) in the activations' type."""
+    (float32 [slots, W] as a strided view); out = S_t * gelu_tanh(y_t + y_bias) in the activations' type.  ``max_q_len``:
+    the longest portion of the step; long ones are walked in stretches side by side (csrc/gated_recurrence.cu)."""
     n, W = decay.shape
     _need(decay.is_contiguous() and drive.is_contiguous() and drive.shape == decay.shape and decay.dtype == drive.dtype == torch.float32,
           "linear_recurrence: decay and drive float32 [n, W]")
@@ -1280,19 +1281,32 @@ def linear_recurrence(decay: torch.Tensor, drive: torch.Tensor, y: torch.Tensor,
     _check(lib().vcb_linear_recurrence(decay.data_ptr(), drive.data_ptr(), decay.stride(0), y.data_ptr(), y.stride(0),
                                        None if y_bias is None else _dev(y_bias, "y_bias", torch.float32), state.data_ptr(),
                                        state.stride(0), out.data_ptr(), out.stride(0), _dev(q_start, "q_start", torch.int32),
-                                       _dev(state_slots, "state_slots", torch.int32), n_reqs, W, dtype_code(out.dtype), _stream()),
-           "linear_recurrence")
+                                       _dev(state_slots, "state_slots", torch.int32), n_reqs, int(max_q_len), W, dtype_code(out.dtype),
+                                       _stream()), "linear_recurrence")
+
+
+DELTA_PORTIONS_FROM = 8       # a step whose longest portion has this many tokens prepares the recurrence's inputs in a kernel of its own
+
+
+def gated_delta_work_row(num_heads: int, num_qk_heads: int, head_dim: int) -> int:
+    """Floats of a token's row of prepared inputs: unit q and k per qk head, a decay per head and key channel, beta per
+    head, q . k per qk head; rounded up to 16 bytes."""
+    return ((2 * num_qk_heads + num_heads) * head_dim + num_heads + num_qk_heads + 3) // 4 * 4
 
 
 def gated_delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta_pre: torch.Tensor, decay_pre: torch.Tensor,
                      a_log: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor, out: torch.Tensor, q_start, state_slots,
-                     n_reqs: int, *, num_heads: int, num_qk_heads: int, q_scale: float, unit_eps: float) -> None:
+                     n_reqs: int, *, num_heads: int, num_qk_heads: int, q_scale: float, unit_eps: float, max_q_len: int = 1,
+                     work: Optional[torch.Tensor] = None) -> None:
     """The gated delta rule per request and head over the step's tokens, S (float32 [dk, dv]) read from and left in the
     request's slot of ``state`` [slots, heads, dk, dv]:
         S <- diag(g_t) S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  out_t = S^T q_t
     q, k float32 rows [n, qk heads * dk] (made unit vectors per head here: x / sqrt(sum x^2 + unit_eps); q times
     ``q_scale``), head h reading qk head h // (heads / qk heads); v float32 rows [n, heads * dv]; beta = sigmoid(beta_pre
-    [n, heads]); g = exp(-exp(a_log[h]) * softplus(decay_pre [n, heads * dk] + dt_bias)); out float32 [n, heads * dv]."""
+    [n, heads]); g = exp(-exp(a_log[h]) * softplus(decay_pre [n, heads * dk] + dt_bias)); out float32 [n, heads * dv].
+    A step whose longest portion ``max_q_len`` reaches DELTA_PORTIONS_FROM tokens runs in two kernels: the unit vectors, decays
+    and betas of all tokens at once into ``work`` (float32, n * gated_delta_work_row(...) elements; made here if absent),
+    then the walk over the tokens, which needs one round of shuffles per token (csrc/gated_recurrence.cu)."""
     n = q.shape[0]
     H, G = num_heads, num_qk_heads
     _need(H % G == 0 and q.shape[1] % G == 0 and v.shape[1] % H == 0, "gated_delta_scan: head counts")
@@ -1306,12 +1320,19 @@ def gated_delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta_pre
     _need(dk <= 1024, "gated_delta_scan: key heads of up to 1024 channels")
     _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (H, dk, dv),
           "gated_delta_scan: state float32 [slots, heads, dk, dv]")
+    portions = max_q_len >= DELTA_PORTIONS_FROM
+    if portions:
+        need = n * gated_delta_work_row(H, G, dk)
+        if work is None:
+            work = torch.empty(need, dtype=torch.float32, device=q.device)
+        _need(work.dtype == torch.float32 and work.is_contiguous() and work.numel() >= need, "gated_delta_scan: work too small")
     _check(lib().vcb_gated_delta_scan(q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), k.stride(0), v.stride(0),
                                       beta_pre.data_ptr(), beta_pre.stride(0), decay_pre.data_ptr(), decay_pre.stride(0),
                                       _dev(a_log, "a_log", torch.float32), _dev(dt_bias, "dt_bias", torch.float32),
                                       state.data_ptr(), out.data_ptr(), out.stride(0), _dev(q_start, "q_start", torch.int32),
                                       _dev(state_slots, "state_slots", torch.int32), n_reqs, H, G, dk, dv, float(q_scale),
-                                      float(unit_eps), dtype_code(beta_pre.dtype), _stream()), "gated_delta_scan")
+                                      float(unit_eps), dtype_code(beta_pre.dtype), work.data_ptr() if portions else None,
+                                      n if portions else 0, _stream()), "gated_delta_scan")
 
 
 # ------------------------------------------------------------------ latent attention

@@ -88,7 +88,8 @@ class RealGatedLinearRecurrence(Mixer):
         drive = ws.take((n, W), torch.float32)
         ops.gate_blocks(u, self.w_ra, self.w_ri, self.b_ra, self.b_ri, self.lam, decay, drive, self.c)
         act = ws.take((n, W), self.dtype)
-        ops.linear_recurrence(decay, drive, proj[:, :W], self.b_y, slots[:, 0], act, step.q_start, step.state_slots, step.n_reqs)
+        ops.linear_recurrence(decay, drive, proj[:, :W], self.b_y, slots[:, 0], act, step.q_start, step.state_slots, step.n_reqs,
+                              step.max_q_len)
         ops.linear(act, self.w_o, out)
         ws.release(mark)
 
@@ -153,7 +154,8 @@ class GatedDeltaRule(Mixer):
         vv = self.H * self.dv
         return (workspace_piece((n_tokens, self.in_width()), self.dtype) + workspace_piece((n_tokens, self.conv_channels), torch.float32)
                 + workspace_piece((n_tokens, self.H * self.dk), self.dtype) + 2 * workspace_piece((n_tokens, vv), self.dtype)
-                + workspace_piece((n_tokens, vv), torch.float32))
+                + workspace_piece((n_tokens, vv), torch.float32)
+                + workspace_piece((n_tokens, ops.gated_delta_work_row(self.H, self.G, self.dk)), torch.float32))
 
     def forward(self, x, out, step, cache, writes_cache, ws):
         n, H, G, dk, dv, C = x.shape[0], self.H, self.G, self.dk, self.dv, self.conv_channels
@@ -172,9 +174,10 @@ class GatedDeltaRule(Mixer):
         ops.causal_conv(proj[:, :C], self.conv, window.slots, qkv, step.q_start, step.state_slots, step.n_reqs, step.max_q_len,
                         act="silu")
         o = ws.take((n, H * dv), torch.float32)
+        work = ws.take((n, ops.gated_delta_work_row(H, G, dk)), torch.float32) if step.max_q_len >= ops.DELTA_PORTIONS_FROM else None
         ops.gated_delta_scan(qkv[:, : G * dk], qkv[:, G * dk: 2 * G * dk], qkv[:, 2 * G * dk:], beta_pre, decay_pre, self.a_log,
                              self.dt_bias, matrix.slots, o, step.q_start, step.state_slots, step.n_reqs, num_heads=H,
-                             num_qk_heads=G, q_scale=float(dk) ** -0.5, unit_eps=UNIT_NORM_EPS)
+                             num_qk_heads=G, q_scale=float(dk) ** -0.5, unit_eps=UNIT_NORM_EPS, max_q_len=step.max_q_len, work=work)
         act = ws.take((n, H * dv), self.dtype)
         ops.gated_group_norm(o, gate_pre, self.w_norm, act, group=dv, eps=self.eps, gate_act="sigmoid")
         ops.linear(act, self.w_o, out)
