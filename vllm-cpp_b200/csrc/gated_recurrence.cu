@@ -606,40 +606,32 @@ delta_walk_kernel(DeltaArgs a, const float* __restrict__ work, long long ldw, in
         const float* vs = gs + TC * tstride;
         const float* bs = vs + TC * DVT;
         if (cl < DVT) {
-            // the rows of the token after this one are read from shared memory while this one's sums run
-            float4 q4[DKP / 4], k4[DKP / 4], g4[DKP / 4], qn[DKP / 4], kn[DKP / 4], gn[DKP / 4];
+            // the rows of the token after this one are read from shared memory while this one's sums run; two sets of
+            // registers take turns, so nothing is copied between them
+            struct Rows { float4 q[DKP / 4], k[DKP / 4], g[DKP / 4]; float beta, qk, v; };
             const float* mine = qs + part * pstride;
+            auto read = [&](Rows& w, int tt) {
+                const float* at = mine + tt * tstride;
 #pragma unroll
-            for (int i = 0; i < DKP / 4; ++i) {
-                qn[i] = reinterpret_cast<const float4*>(mine)[i];
-                kn[i] = reinterpret_cast<const float4*>(mine + TC * tstride)[i];
-                gn[i] = reinterpret_cast<const float4*>(mine + 2 * TC * tstride)[i];
-            }
-            float beta_n = bs[0], qk_n = bs[1], v_n = col_ok ? vs[cl] : 0.0f;
-            for (int tt = 0; tt < tc; ++tt) {
-#pragma unroll
-                for (int i = 0; i < DKP / 4; ++i) { q4[i] = qn[i]; k4[i] = kn[i]; g4[i] = gn[i]; }
-                const float beta = beta_n, qk = qk_n, vv = v_n;
-                if (tt + 1 < tc) {
-                    const float* next = mine + (tt + 1) * tstride;
-#pragma unroll
-                    for (int i = 0; i < DKP / 4; ++i) {
-                        qn[i] = reinterpret_cast<const float4*>(next)[i];
-                        kn[i] = reinterpret_cast<const float4*>(next + TC * tstride)[i];
-                        gn[i] = reinterpret_cast<const float4*>(next + 2 * TC * tstride)[i];
-                    }
-                    beta_n = bs[2 * tt + 2];
-                    qk_n = bs[2 * tt + 3];
-                    v_n = col_ok ? vs[(tt + 1) * DVT + cl] : 0.0f;
+                for (int i = 0; i < DKP / 4; ++i) {
+                    w.q[i] = reinterpret_cast<const float4*>(at)[i];
+                    w.k[i] = reinterpret_cast<const float4*>(at + TC * tstride)[i];
+                    w.g[i] = reinterpret_cast<const float4*>(at + 2 * TC * tstride)[i];
                 }
+                w.beta = bs[2 * tt];
+                w.qk = bs[2 * tt + 1];
+                w.v = col_ok ? vs[tt * DVT + cl] : 0.0f;
+            };
+            auto token = [&](const Rows& w, Rows& next, int tt) {
+                if (tt + 1 < tc) read(next, tt + 1);
                 float p0 = 0.0f, p1 = 0.0f, p2 = 0.0f, p3 = 0.0f, r0 = 0.0f, r1 = 0.0f, r2 = 0.0f, r3 = 0.0f;
 #pragma unroll
                 for (int i = 0; i < DKP / 4; ++i) {
-                    S[4 * i] *= g4[i].x; S[4 * i + 1] *= g4[i].y; S[4 * i + 2] *= g4[i].z; S[4 * i + 3] *= g4[i].w;
-                    p0 = fmaf(S[4 * i], k4[i].x, p0);     r0 = fmaf(S[4 * i], q4[i].x, r0);
-                    p1 = fmaf(S[4 * i + 1], k4[i].y, p1); r1 = fmaf(S[4 * i + 1], q4[i].y, r1);
-                    p2 = fmaf(S[4 * i + 2], k4[i].z, p2); r2 = fmaf(S[4 * i + 2], q4[i].z, r2);
-                    p3 = fmaf(S[4 * i + 3], k4[i].w, p3); r3 = fmaf(S[4 * i + 3], q4[i].w, r3);
+                    S[4 * i] *= w.g[i].x; S[4 * i + 1] *= w.g[i].y; S[4 * i + 2] *= w.g[i].z; S[4 * i + 3] *= w.g[i].w;
+                    p0 = fmaf(S[4 * i], w.k[i].x, p0);     r0 = fmaf(S[4 * i], w.q[i].x, r0);
+                    p1 = fmaf(S[4 * i + 1], w.k[i].y, p1); r1 = fmaf(S[4 * i + 1], w.q[i].y, r1);
+                    p2 = fmaf(S[4 * i + 2], w.k[i].z, p2); r2 = fmaf(S[4 * i + 2], w.q[i].z, r2);
+                    p3 = fmaf(S[4 * i + 3], w.k[i].w, p3); r3 = fmaf(S[4 * i + 3], w.q[i].w, r3);
                 }
                 float p = (p0 + p1) + (p2 + p3), rr = (r0 + r1) + (r2 + r3);
 #pragma unroll
@@ -649,15 +641,21 @@ delta_walk_kernel(DeltaArgs a, const float* __restrict__ work, long long ldw, in
                         rr += __shfl_xor_sync(0xffffffffu, rr, o);
                     }
                 }
-                const float u = beta * (vv - p);
+                const float u = w.beta * (w.v - p);
 #pragma unroll
                 for (int i = 0; i < DKP / 4; ++i) {
-                    S[4 * i] = fmaf(k4[i].x, u, S[4 * i]);
-                    S[4 * i + 1] = fmaf(k4[i].y, u, S[4 * i + 1]);
-                    S[4 * i + 2] = fmaf(k4[i].z, u, S[4 * i + 2]);
-                    S[4 * i + 3] = fmaf(k4[i].w, u, S[4 * i + 3]);
+                    S[4 * i] = fmaf(w.k[i].x, u, S[4 * i]);
+                    S[4 * i + 1] = fmaf(w.k[i].y, u, S[4 * i + 1]);
+                    S[4 * i + 2] = fmaf(w.k[i].z, u, S[4 * i + 2]);
+                    S[4 * i + 3] = fmaf(w.k[i].w, u, S[4 * i + 3]);
                 }
-                if (part == 0) os[tt * DVT + cl] = fmaf(qk, u, rr);
+                if (part == 0) os[tt * DVT + cl] = fmaf(w.qk, u, rr);
+            };
+            Rows even, odd;
+            read(even, 0);
+            for (int tt = 0; tt < tc; tt += 2) {
+                token(even, odd, tt);
+                if (tt + 1 < tc) token(odd, even, tt + 1);
             }
         }
         __syncthreads();
