@@ -364,6 +364,7 @@ def test_a_key_written_long_before_it_is_asked_for(H, G, dk, dv, planted_at, cut
     ("float32", 2, 1, 8, 8, rot(8, 20.0), 32, True), ("bfloat16", 6, 2, 64, 64, rot(32, 1e4, (5.0, 1.0, 3.0, 128)), 16, False),
     ("bfloat16", 6, 2, 64, 64, rot(32, 1e4, (5.0, 1.0, 3.0, 128)), 16, True), ("bfloat16", 2, 1, 128, 128, rot(128, 1e5), 32, False),
     ("bfloat16", 20, 1, 64, 64, None, 16, False), ("bfloat16", 4, 4, 128, 128, rot(64, 500.0), 16, False),
+    ("bfloat16", 8, 2, 64, 64, rot(32, 2e4, (3.0, 1.0, 2.0, 64)), 16, False), ("bfloat16", 16, 8, 128, 128, rot(16, 30.0), 32, False),
     ("bfloat16", 5, 1, 48, 80, rot(24, 50.0, (2.0, 0.5, 8.0, 16)), 16, True), ("float32", 8, 8, 16, 16, rot(2, 7.0), 16, True)])
 def test_attention_with_a_sink_and_a_planted_key(dtype, H, G, dk, dv, rotation, page, plain_kernel):
     """The mixer itself (its products are identities, so its input rows are q, k, v and the gate's logits) through the
