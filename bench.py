@@ -1176,9 +1176,9 @@ def lutodra_attention_kernels(z, peaks, add, rnd):
     kv = rnd(n_pages, 2, nkv, page * d, scale=0.5)
     sink, gate = rnd(nh, dtype=torch.float32), rnd(t, nh)
     seen = t * (t + 1) // 2
-    for epi, name, like in ((True, f"attention with sink and head gate, prompt of {t}", ""),
+    for epi, name, like in ((True, f"attention with sink, head gate and two-term weights, prompt of {t}", ""),
                             (False, f"Qwen2: attention, prompt of {t}", "like the one above")):
-        kw = dict(sink=sink, head_gate=gate) if epi else {}
+        kw = dict(sink=sink, head_gate=gate, precise_weights=True) if epi else {}
         add(name, like, lambda i: ops.attention_prefill_tc(q, kv, o, q_start, ctx, bt, tile_req, tile_row0, num_heads=nh, num_kv_heads=nkv, head_dim=d,
                                                            page_size=page, window=0, scale=d ** -0.5, **kw), 4, flops=4.0 * nh * d * seen)
     part = PagedAttention(h, nh, nkv, d, True, False, 0, PartSpec("none"), bf, dev)
@@ -1196,9 +1196,9 @@ def lutodra_attention_kernels(z, peaks, add, rnd):
         q, o = rnd(batch, nh * d), torch.empty(batch, nh * d, dtype=bf, device=dev)
         kv = rnd(batch * blocks + 1, 2, nkv, page * d, scale=0.5)
         gate = rnd(batch, nh)
-        for epi, name, like in ((True, f"attention with sink and head gate, decode, batch {batch}, context {LUTODRA_CONTEXT}", ""),
+        for epi, name, like in ((True, f"attention with sink, head gate and two-term weights, decode, batch {batch}, context {LUTODRA_CONTEXT}", ""),
                                 (False, f"Qwen2: attention, decode, batch {batch}, context {LUTODRA_CONTEXT}", "like the one above")):
-            kw = dict(sink=sink, head_gate=gate) if epi else {}
+            kw = dict(sink=sink, head_gate=gate, precise_weights=True) if epi else {}
             add(name, like, lambda i: ops.attention_decode_mma(q, kv, o, q_start, ctx, bt, None, batch, nsplit, po, pml, tickets, num_heads=nh,
                                                                num_kv_heads=nkv * share, head_dim=d, page_size=page, window=0, scale=d ** -0.5,
                                                                split_tiles=split_tiles, kv_share=share, **kw), 4,

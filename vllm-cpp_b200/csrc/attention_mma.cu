@@ -67,6 +67,9 @@ struct MmaAttnArgs {
     const float* sink;
     const __nv_bfloat16* gate;
     long long ldg;
+    // Nonzero: the softmax weights enter the P V product as two bfloat16 terms, p = hi + lo with hi the rounding of p and lo
+    // that of the rest (16 bits of mantissa instead of 8), for designs that want their attention weights in 32-bit.
+    int precise_weights;
 };
 
 // 1 / (l + e^(sink - m)) * sigmoid(gate): what an output row is multiplied by.  m2: the reference of l in units of log2.
@@ -441,6 +444,15 @@ attention_decode_kernel(MmaAttnArgs a) {
                 pf[0][0] = pack_bf16(p[0][0], p[0][1]); pf[0][1] = pack_bf16(p[0][2], p[0][3]);
                 pf[0][2] = pack_bf16(p[1][0], p[1][1]); pf[0][3] = pack_bf16(p[1][2], p[1][3]);
                 pv_product<D, BN, 1>(o, pf, sv, warp * 16);
+                if (a.precise_weights) {
+                    auto rest = [](float x, float y) {
+                        const __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
+                        return pack_bf16(x - __low2float(h), y - __high2float(h));
+                    };
+                    pf[0][0] = rest(p[0][0], p[0][1]); pf[0][1] = rest(p[0][2], p[0][3]);
+                    pf[0][2] = rest(p[1][0], p[1][1]); pf[0][3] = rest(p[1][2], p[1][3]);
+                    pv_product<D, BN, 1>(o, pf, sv, warp * 16);
+                }
                 __syncwarp();
                 if (lane == 0) cx_mbar_arrive(empty0 + 8 * st);      // this warp is done with the stage
             }
@@ -678,9 +690,11 @@ __host__ __device__ constexpr uint32_t idesc(int n, bool b_mn) {
     return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn ? (1u << 16) : 0u) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
 
-template <int D>
+template <int D, bool PRECISE>
 __global__ void __launch_bounds__(THREADS, 2)
 attention_prefill_tc_kernel(MmaAttnArgs a) {
+    // PRECISE (a template parameter of this kernel): the weights' rest after their rounding to bfloat16 goes into the second
+    // half of the S buffer, whose scores have been read by then, and a second P V product adds it.
     static_assert(D == 64 || D == 128, "one or two planes of 64 elements; S, S and O fit 256 columns");
     constexpr int Q_BYTES = BMT * D * 2, KV_BYTES = TKT * D * 2, K_STAGES = k_stages<D>(), V_STAGES = v_stages<D>();
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -803,6 +817,11 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
 #pragma unroll
                     for (int kk = 0; kk < TKT / 16; ++kk)       // 16 keys a step: eight columns of P
                         mma_ts(tm_o, tm_p + kk * 8, desc_mn(v_base + kk * 16 * 128, TKT * 128), id_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                    if (PRECISE) {
+#pragma unroll
+                        for (int kk = 0; kk < TKT / 16; ++kk)
+                            mma_ts(tm_o, tm_p + TKT / 2 + kk * 8, desc_mn(v_base + kk * 16 * 128, TKT * 128), id_pv, 1u);
+                    }
                     commit(B(PV_DONE));         // P read, O updated
                     commit(B(EMPTY_V + vs));    // V stage free
                     if (j == n_tiles - 1) commit(B(O_DONE));
@@ -931,7 +950,7 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
                 m_ref = mt;
             }
             const float base = m_ref == -INFINITY ? 0.0f : m_ref * sl2;
-            uint32_t pk[TKT / 2];
+            uint32_t pk[TKT / 2], pl[TKT / 2];          // pl: the weights' rests (PRECISE only; unused otherwise)
             const uint64_t scale2 = pack2(sl2, sl2), minus_base2 = pack2(-base, -base);
             uint64_t sum2[2] = {pack2(0.0f, 0.0f), pack2(0.0f, 0.0f)};
 #pragma unroll
@@ -941,6 +960,10 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
                 const float p0 = fast_exp2(e0), p1 = fast_exp2(e1);
                 sum2[(i >> 1) & 1] = add2(sum2[(i >> 1) & 1], pack2(p0, p1));
                 pk[i >> 1] = pack_bf16(p0, p1);
+                if (PRECISE) {
+                    const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&pk[i >> 1]);
+                    pl[i >> 1] = pack_bf16(p0 - __low2float(hi), p1 - __high2float(hi));
+                }
             }
             float lt;
             {
@@ -969,6 +992,7 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
             // P over the row's own scores (this thread has read them; the tensor cores write these columns
             // again only with the scores of tile j + 2, after the P V that reads P)
             st32u(s_addr, pk);
+            if (PRECISE) st32u(s_addr + TKT / 2, pl);
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             // the four warps arrive on one barrier per tile: a warp that runs ahead must not count towards
             // a tile that another warp has not finished
@@ -1009,12 +1033,17 @@ attention_prefill_tc_kernel(MmaAttnArgs a) {
 }
 }  // namespace tc
 
+template <int D, bool PRECISE>
+static int launch_prefill_tc_as(const MmaAttnArgs& a, int n_tiles, cudaStream_t s) {
+    static unsigned long long configured = 0;
+    if (int e = vcb_allow_dynamic_smem(tc::attention_prefill_tc_kernel<D, PRECISE>, tc::smem_bytes<D>(), &configured)) return e;
+    vcb_launch(tc::attention_prefill_tc_kernel<D, PRECISE>, dim3((unsigned)n_tiles * a.nkv), tc::THREADS, (size_t)tc::smem_bytes<D>(), s, a);
+    return vcb_last_error();
+}
+
 template <int D>
 static int launch_prefill_tc(const MmaAttnArgs& a, int n_tiles, cudaStream_t s) {
-    static unsigned long long configured = 0;
-    if (int e = vcb_allow_dynamic_smem(tc::attention_prefill_tc_kernel<D>, tc::smem_bytes<D>(), &configured)) return e;
-    vcb_launch(tc::attention_prefill_tc_kernel<D>, dim3((unsigned)n_tiles * a.nkv), tc::THREADS, (size_t)tc::smem_bytes<D>(), s, a);
-    return vcb_last_error();
+    return a.precise_weights ? launch_prefill_tc_as<D, true>(a, n_tiles, s) : launch_prefill_tc_as<D, false>(a, n_tiles, s);
 }
 
 // Both kernels copy a tile of 64 keys as at most eight runs of whole pages' rows (tile_piece: one lane
@@ -1057,7 +1086,7 @@ VCB_EXPORT int vcb_attention_decode_mma_shaped(const void* q, const void* cache,
                                                float* part_ml, int* counters, const int* split_tiles, int nh, int nkv,
                                                int d, int page, int window, float scale, int num_pages, int* status,
                                                int kv_share, float cap, const float* bias_t, int bias_len, const float* sink,
-                                               const void* gate, long long ldg, void* stream) {
+                                               const void* gate, long long ldg, int precise_weights, void* stream) {
     if (n_list <= 0) return 0;
     int c = check_common(nh, nkv, d, page, window, num_pages);
     if (c) return c;
@@ -1065,7 +1094,8 @@ VCB_EXPORT int vcb_attention_decode_mma_shaped(const void* q, const void* cache,
     if (nsplit < 1 || nsplit > 32 || (nsplit > 1 && (!part_o || !part_ml || !counters))) return VCB_ERR_BAD_ARG;
     MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
                   block_table, req_list, nullptr, part_o, part_ml, counters, status, split_tiles, bt_stride, nh, nkv,
-                  page, window, scale, num_pages, 2, kv_share, cap, bias_t, bias_len, sink, (const __nv_bfloat16*)gate, ldg};
+                  page, window, scale, num_pages, 2, kv_share, cap, bias_t, bias_len, sink, (const __nv_bfloat16*)gate, ldg,
+                  precise_weights};
     cudaStream_t s = (cudaStream_t)stream;
     return d == 64 ? launch_decode<64>(a, n_list, nsplit, s) : launch_decode<128>(a, n_list, nsplit, s);
 }
@@ -1105,14 +1135,14 @@ VCB_EXPORT int vcb_attention_prefill_tc_shaped(const void* q, const void* cache,
                                                const int* tile_req, const int* tile_row0, int n_tiles, int nh,
                                                int nkv, int d, int page, int window, float scale, int num_pages,
                                                int* status, float cap, const float* bias_t, int bias_len, const float* sink,
-                                               const void* gate, long long ldg, void* stream) {
+                                               const void* gate, long long ldg, int precise_weights, void* stream) {
     if (n_tiles <= 0) return 0;
     int c = check_common(nh, nkv, d, page, window, num_pages);
     if (c) return c;
     if (bias_t && bias_len <= 0) return VCB_ERR_BAD_ARG;
     MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
                   block_table, tile_req, tile_row0, nullptr, nullptr, nullptr, status, nullptr, bt_stride, nh, nkv, page,
-                  window, scale, num_pages, 2, 1, cap, bias_t, bias_len, sink, (const __nv_bfloat16*)gate, ldg};
+                  window, scale, num_pages, 2, 1, cap, bias_t, bias_len, sink, (const __nv_bfloat16*)gate, ldg, precise_weights};
     return d == 64 ? launch_prefill_tc<64>(a, n_tiles, (cudaStream_t)stream) : launch_prefill_tc<128>(a, n_tiles, (cudaStream_t)stream);
 }
 

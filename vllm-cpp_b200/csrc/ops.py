@@ -55,8 +55,8 @@ _SIGNATURES = {
     "vcb_headwise_linear": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "vcb_sigmoid_gate": [_P, _P, _I, _I, _I, _I, _I, _P],
     "vcb_attention_decode_mma_shaped": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _I, _F, _P, _I,
-                                        _P, _P, _L, _P],
-    "vcb_attention_prefill_tc_shaped": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _F, _P, _I, _P, _P, _L, _P],
+                                        _P, _P, _L, _I, _P],
+    "vcb_attention_prefill_tc_shaped": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _F, _P, _I, _P, _P, _L, _I, _P],
     "vcb_embedding_scaled": [_P, _P, _P, _I, _I, _I, _P, _F, _I, _P],
     "vcb_norm_residual_norm": [_P, _P, _P, _P, _P, _I, _I, _F, _F, _I, _P],
     "vcb_decayed_state_scan": [_P, _P, _P, _P, _L, _L, _L, _L, _P, _P, _F, _F, _I, _P, _P, _L, _P, _P, _I, _I, _I, _I, _I, _P, _L, _P, _I, _P],
@@ -286,7 +286,7 @@ def attention_decode_mma(q, cache, out, q_start, ctx_lens, block_table, req_list
                          part_o, part_ml, counters, *, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
                          window: int, scale: float, split_tiles=None, planes: int = 2, kv_share: int = 1,
                          cap: float = 0.0, bias_t: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None,
-                         head_gate: Optional[torch.Tensor] = None) -> None:
+                         head_gate: Optional[torch.Tensor] = None, precise_weights: bool = False) -> None:
     """Split-KV tensor-core attention for requests that bring one token each (bfloat16).  The grid has
     ``nsplit`` columns; without ``split_tiles`` every request's keys are cut into that many equal parts,
     with it (int32 [1] on the device: tiles of DECODE_KEY_TILE keys per split) a request takes as many
@@ -304,7 +304,8 @@ def attention_decode_mma(q, cache, out, q_start, ctx_lens, block_table, req_list
               "attention_decode_mma: scratch for the split merge is too small")
     _need(planes in (1, 2), "planes must be 1 or 2")
     _need(kv_share >= 1 and num_kv_heads % kv_share == 0, "attention_decode_mma: kv_share divides num_kv_heads")
-    if cap > 0 or bias_t is not None or sink is not None or head_gate is not None:
+    if cap > 0 or bias_t is not None or sink is not None or head_gate is not None or precise_weights:
+        # ``precise_weights``: the softmax weights enter the P V product as two bfloat16 terms (16 bits of mantissa)
         # shaped scores: cap * tanh(scale * q.k / cap) + bias_t[head, min(distance, last)]; the epilogue: a sink logit per
         # head in the denominator, the head's output times sigmoid(head_gate[token, head]) (see attention_mma.cu)
         _need(planes == 2, "attention_decode_mma: shaped scores come with keys and values in planes of their own")
@@ -321,7 +322,7 @@ def attention_decode_mma(q, cache, out, q_start, ctx_lens, block_table, req_list
             num_heads, num_kv_heads, head_dim, page_size, window, float(scale), cache.shape[0],
             status_tensor(q.device).data_ptr(), kv_share, float(cap),
             None if bias_t is None else _dev(bias_t, "bias_t", torch.float32), 0 if bias_t is None else bias_t.shape[1],
-            *_epilogue_ptrs(sink, head_gate), _stream()), "attention_decode_mma")
+            *_epilogue_ptrs(sink, head_gate), 1 if precise_weights else 0, _stream()), "attention_decode_mma")
         return
     _check(lib().vcb_attention_decode_mma_planes(
         _dev(q, "q"), _dev(cache, "cache"), _dev(out, "out"), _dev(q_start, "q_start", torch.int32),
@@ -353,7 +354,8 @@ TC_ATTENTION_TILE_ROWS = 128     # packed rows per tile of its work list
 def attention_prefill_tc(q, cache, out, q_start, ctx_lens, block_table, tile_req, tile_row0, *,
                          num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int,
                          scale: float, planes: int = 2, cap: float = 0.0, bias_t: Optional[torch.Tensor] = None,
-                         sink: Optional[torch.Tensor] = None, head_gate: Optional[torch.Tensor] = None) -> None:
+                         sink: Optional[torch.Tensor] = None, head_gate: Optional[torch.Tensor] = None,
+                         precise_weights: bool = False) -> None:
     """Attention for portions of any length on tcgen05 tensor cores (scores and output tiles in tensor
     memory); head sizes 64 and 128, bfloat16, pages of a multiple of 8 slots, tiles of 128 packed rows."""
     _need(q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
@@ -363,7 +365,7 @@ def attention_prefill_tc(q, cache, out, q_start, ctx_lens, block_table, tile_req
     n_tiles = tile_req.numel()
     _need(tile_row0.numel() == n_tiles, "one first row per tile")
     _need(planes in (1, 2), "planes must be 1 or 2")
-    if cap > 0 or bias_t is not None or sink is not None or head_gate is not None:
+    if cap > 0 or bias_t is not None or sink is not None or head_gate is not None or precise_weights:
         _need(planes == 2, "attention_prefill_tc: shaped scores come with keys and values in planes of their own")
         _need(bias_t is None or (bias_t.dim() == 2 and bias_t.shape[0] == num_heads), "attention_prefill_tc: bias_t [heads, distances]")
         _epilogue_args(sink, head_gate, q.shape[0], num_heads, "attention_prefill_tc")
@@ -373,7 +375,7 @@ def attention_prefill_tc(q, cache, out, q_start, ctx_lens, block_table, tile_req
             block_table.shape[1], _dev(tile_req, "tile_req", torch.int32), _dev(tile_row0, "tile_row0", torch.int32),
             n_tiles, num_heads, num_kv_heads, head_dim, page_size, window, float(scale), cache.shape[0],
             status_tensor(q.device).data_ptr(), float(cap), None if bias_t is None else _dev(bias_t, "bias_t", torch.float32),
-            0 if bias_t is None else bias_t.shape[1], *_epilogue_ptrs(sink, head_gate), _stream()), "attention_prefill_tc")
+            0 if bias_t is None else bias_t.shape[1], *_epilogue_ptrs(sink, head_gate), 1 if precise_weights else 0, _stream()), "attention_prefill_tc")
         return
     _check(lib().vcb_attention_prefill_tc_planes(
         _dev(q, "q"), _dev(cache, "cache"), _dev(out, "out"), _dev(q_start, "q_start", torch.int32),

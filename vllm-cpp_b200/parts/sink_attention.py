@@ -10,8 +10,9 @@ The sink is a learned logit per head that takes part in the denominator only: it
 scaled, and counts once.  ``window`` > 0 restricts the keys to the last ``window``.  q, k, v and the gate are one product;
 norm, rotation and the cache write are one kernel (csrc/attention_biased.cu, qk_head_rope_cache_write_kernel); bfloat16
 heads of 64 or 128 with keys as wide as values run the tensor-core kernels (csrc/attention_mma.cu: tcgen05 for portions,
-split-KV for single tokens) with the sink and the gate in their epilogues, everything else the plain paged kernel of
-attention_biased.cu, which has them too.  The cache holds rows of
+split-KV for single tokens) with the sink and the gate in their epilogues and, with ``precise_weights``, the softmax
+weights as two bfloat16 terms in the product with the values (the weights are float up to there; one term would round them
+to 8 bits of mantissa); everything else runs the plain paged kernel of attention_biased.cu, whose weights stay float.  The cache holds rows of
 max(head_dim, v_head_dim) elements.  The reference's attention (src/layers/attention.cpp) has rotation and none of the
 rest.
 """
@@ -31,7 +32,7 @@ from .base import POSITION_ENCODINGS, PagedKVSpec, ParamSpec, build_part, regist
 class SinkAttention(PagedAttentionKernels):
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int, scale: float,
                  eps: float, position: PartSpec, dtype, device, window: int = 0, qk_norm: bool = True, sink: bool = True,
-                 head_gate: bool = True):
+                 head_gate: bool = True, precise_weights: bool = True):
         if min(hidden_size, num_heads, num_kv_heads, head_dim, v_head_dim) <= 0 or num_heads % num_kv_heads:
             raise ValueError(f"sink_attention: {num_heads} heads cannot share {num_kv_heads} kv heads")
         if v_head_dim > 256 or head_dim > 1024:
@@ -43,6 +44,7 @@ class SinkAttention(PagedAttentionKernels):
         self.d = self.row
         self.scale, self.window, self.eps = float(scale), int(window), float(eps)
         self.qk_norm, self.has_sink, self.head_gate = bool(qk_norm), bool(sink), bool(head_gate)
+        self.precise_weights = bool(precise_weights)
         self.dtype, self.device = dtype, device
         self.position = build_part(POSITION_ENCODINGS, "position encoding", position, dtype=dtype, device=device)
         fused = self.position.fused()
@@ -59,7 +61,8 @@ class SinkAttention(PagedAttentionKernels):
         return self.dk == self.dv and super()._tensor_core_path()
 
     def score_shaping(self):
-        return {"sink": self.sink} if self.has_sink else {}
+        # the design wants its attention weights in 32-bit: the tensor-core kernels take them as two bfloat16 terms
+        return dict({"sink": self.sink} if self.has_sink else {}, precise_weights=self.precise_weights)
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         specs = {"q": ParamSpec((self.nh * self.dk, self.hidden)), "k": ParamSpec((self.nkv * self.dk, self.hidden)),
