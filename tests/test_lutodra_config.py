@@ -78,6 +78,16 @@ def test_config_is_read_and_described_as_parts():
     assert resolve_architecture(SAMPLE, "lutodra")[1].architecture == "Lutodra"
 
 
+def test_where_the_logit_scale_goes():
+    """A power of two rides in the final norm (it commutes with every rounding); any other factor multiplies the
+    float32 logits after the product."""
+    from vllm_cpp_b200.config.registry import resolve_architecture
+    for scale, in_norm in ((0.5, True), (4.0, True), (1.0, True), (3.0, False), (0.37, False)):
+        _, spec = resolve_architecture(config([rglru(8, 1)], width=8, vocab=9, logit_scale=scale))
+        assert spec.final_norm.params["out_scale"] == (scale if in_norm else 1.0)
+        assert spec.model_params.get("logit_scale", 1.0) == (1.0 if in_norm else scale)
+
+
 def test_what_a_config_may_leave_out():
     """No ``streams``: one plain residual stream without mixing tensors; no ``loop``: every layer once; no rotation,
     no scaling, no groups."""

@@ -21,6 +21,7 @@ in the weights' sum) is named here or in the parts.  The reference has no model 
 """
 from __future__ import annotations
 
+import math
 from dataclasses import dataclass, field
 from typing import List, Optional
 
@@ -202,13 +203,21 @@ def lutodra_model_spec(c: LutodraConfig) -> ModelSpec:
         ))
     # every pass of a looped layer is an entry of the run order with a cache layer of its own
     order = [LayerCall(layer=li, cache=n) for n, li in enumerate(c.run_order())]
+    # logits = head x * logit_scale.  A power of two commutes with every rounding, so it rides in the final norm for nothing;
+    # any other factor multiplies the float32 logits themselves, after the product (folded into the norm it would be rounded
+    # to the activations' type with x)
+    mantissa, _ = math.frexp(c.logit_scale)
+    in_norm = mantissa == 0.5
+    params = {"streams": c.streams or 1}
+    if not in_norm:
+        params["logit_scale"] = c.logit_scale
     return ModelSpec(
         architecture="Lutodra",
         hidden_size=c.width,
         vocab_size=c.vocab,
         layers=layers,
         run_order=order,
-        final_norm=PartSpec("layernorm", {"size": c.width, "eps": c.eps, "tensor_name": "", "out_scale": c.logit_scale}),
+        final_norm=PartSpec("layernorm", {"size": c.width, "eps": c.eps, "tensor_name": "", "out_scale": c.logit_scale if in_norm else 1.0}),
         tie_word_embeddings=False,
         max_position_embeddings=MAX_POSITIONS,
         embed_name="embed",
@@ -218,7 +227,7 @@ def lutodra_model_spec(c: LutodraConfig) -> ModelSpec:
         init_std=0.05,
         init_gain_std=0.05,
         model_class="stream_decoder",
-        model_params={"streams": c.streams or 1},
+        model_params=params,
     )
 
 

@@ -255,6 +255,7 @@ class StreamDecoderModel(DecoderModel):
 
     def __init__(self, spec, dtype, device):
         self.streams = int(spec.model_params.get("streams", 1))
+        self.logit_scale = float(spec.model_params.get("logit_scale", 1.0))     # on the float32 logits, after the product
         super().__init__(spec, dtype, device)
         if not hasattr(self.final_norm, "forward_streams"):
             raise ValueError("stream_decoder: the final norm must read several streams (forward_streams)")
@@ -272,6 +273,11 @@ class StreamDecoderModel(DecoderModel):
     def embed_tokens(self, step, residual):
         for s in range(self.streams):
             ops.embedding(self.embed, step.token_ids, residual[s])
+
+    def head(self, normed, out):
+        super().head(normed, out)
+        if self.logit_scale != 1.0:
+            ops.scaled_sum(out, out, out, self.logit_scale, 0.0)
 
     def final_rows(self, residual, delta, normed, step):
         if delta is not None:
