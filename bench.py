@@ -1077,7 +1077,7 @@ def lutodra_kernels(z, peaks):
         add(f"Retodra: post norm + layer scale + addition + next norm, {t} tokens", "like the one above",
             lambda i: ops.norm_residual_norm(y[i % c], gain, x1[i % c], 1e-6, next_gain=gain, next_out=o1[i % c], next_eps=1e-6), c, bytes_=t * h * 12)
     # ---- the short convolutions and the recurrent unit: single tokens of a batch, then a prompt
-    for n_reqs, per in ((64, 1), (1, LUTODRA_PROMPT)):
+    for n_reqs, per in ((8, 1), (64, 1), (1, LUTODRA_PROMPT)):
         t, c = n_reqs * per, 3
         what = f"decode, batch {n_reqs}" if per == 1 else f"prompt of {per}"
         q_start = torch.arange(0, t + 1, per, dtype=torch.int32, device=dev)

@@ -184,6 +184,73 @@ gate_blocks_kernel(const float* __restrict__ u, long long ldu, const T* __restri
     }
 }
 
+// The same for a few tokens (single tokens of a batch) and blocks of up to GATE_ROWS_BS channels: the tiles above would
+// fill a fraction of the SMs and walk the block's inputs in dependent slices.  A warp per output channel: its lanes split
+// the block's inputs and keep their weights of both matrices in registers, every token costs two warp sums, and lane t % 32
+// finishes token t (gates, decay, drive).
+constexpr int GATE_ROWS_MAX = 16, GATE_ROWS_BS = 256;      // measured: at 64 tokens the tiles above are faster (29 against 42 us)
+template <typename T>
+__global__ void __launch_bounds__(256)
+gate_rows_kernel(const float* __restrict__ u, long long ldu, const T* __restrict__ wa, const T* __restrict__ wi,
+                 const float* __restrict__ ba, const float* __restrict__ bi, const float* __restrict__ lam,
+                 float* __restrict__ decay, float* __restrict__ drive, long long ldo, int n, int bs, float c_gate) {
+    constexpr int M = GATE_ROWS_BS / 32;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int b = blockIdx.y, cb = blockIdx.x * 8 + warp;
+    const bool live = cb < bs;
+    const int c = b * bs + (live ? cb : 0);
+    float wa_r[M], wi_r[M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+        const int k = lane + 32 * m;
+        const bool ok = live && k < bs;
+        wa_r[m] = ok ? to_f32<T>(wa[((size_t)b * bs + cb) * bs + k]) : 0.0f;
+        wi_r[m] = ok ? to_f32<T>(wi[((size_t)b * bs + cb) * bs + k]) : 0.0f;
+    }
+    const float bav = ba[c], biv = bi[c], sp = gr_softplus(lam[c]);
+    pdl_start();
+    if (!live) return;
+    const float* ub = u + (size_t)b * bs;
+    for (int t0 = 0; t0 < n; t0 += 32) {
+        float mine_a = 0.0f, mine_i = 0.0f;
+        const int t1 = min(t0 + 32, n);
+        for (int t = t0; t < t1; t += 4) {          // four tokens' loads and sums in flight
+            float sa[4], si[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                sa[q] = si[q] = 0.0f;
+                const int tq = min(t + q, t1 - 1);
+#pragma unroll
+                for (int m = 0; m < M; ++m) {
+                    const int k = lane + 32 * m;
+                    if (k < bs) {
+                        const float uv = ub[(size_t)tq * ldu + k];
+                        sa[q] = fmaf(uv, wa_r[m], sa[q]);
+                        si[q] = fmaf(uv, wi_r[m], si[q]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    sa[q] += __shfl_xor_sync(0xffffffffu, sa[q], o);
+                    si[q] += __shfl_xor_sync(0xffffffffu, si[q], o);
+                }
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                if (lane == t + q - t0) { mine_a = sa[q]; mine_i = si[q]; }
+        }
+        const int t = t0 + lane;
+        if (t < t1) {
+            const float r = gr_sigmoid(mine_a + bav), g = gr_sigmoid(mine_i + biv);
+            const float la = -c_gate * r * sp;
+            decay[(size_t)t * ldo + c] = expf(la);
+            drive[(size_t)t * ldo + c] = sqrtf(-expm1f(2.0f * la)) * g * u[(size_t)t * ldu + c];
+        }
+    }
+}
+
 VCB_EXPORT int vcb_gate_blocks(const float* u, long long ldu, const void* wa, const void* wi, const float* ba, const float* bi,
                                const float* lam, float* decay, float* drive, long long ldo, int n, int W, int B, float c_gate,
                                int dtype, void* stream) {
@@ -191,8 +258,18 @@ VCB_EXPORT int vcb_gate_blocks(const float* u, long long ldu, const void* wa, co
     if (!u || !wa || !wi || !ba || !bi || !lam || !decay || !drive || W <= 0 || B <= 0 || W % B) return VCB_ERR_BAD_ARG;
     const int bs = W / B, tiles = (bs + 63) / 64;
     if ((long long)B * tiles > 65535) return VCB_ERR_UNSUPPORTED;
-    dim3 grid((n + 63) / 64, B * tiles);
     cudaStream_t s = (cudaStream_t)stream;
+    if (n <= GATE_ROWS_MAX && bs <= GATE_ROWS_BS && B <= 65535) {
+        dim3 rows((bs + 7) / 8, B);
+        if (dtype == VCB_F32)
+            vcb_launch(gate_rows_kernel<float>, rows, 256, 0, s, u, ldu, (const float*)wa, (const float*)wi, ba, bi, lam, decay, drive, ldo, n, bs, c_gate);
+        else if (dtype == VCB_BF16)
+            vcb_launch(gate_rows_kernel<__nv_bfloat16>, rows, 256, 0, s, u, ldu, (const __nv_bfloat16*)wa, (const __nv_bfloat16*)wi, ba, bi,
+                       lam, decay, drive, ldo, n, bs, c_gate);
+        else return VCB_ERR_BAD_ARG;
+        return vcb_last_error();
+    }
+    dim3 grid((n + 63) / 64, B * tiles);
     if (dtype == VCB_F32)
         vcb_launch(gate_blocks_kernel<float>, grid, 256, 0, s, u, ldu, (const float*)wa, (const float*)wi, ba, bi, lam, decay, drive, ldo, n, bs, tiles, c_gate);
     else if (dtype == VCB_BF16)
