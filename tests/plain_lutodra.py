@@ -225,6 +225,8 @@ def attention_mixer(w, p, m, h, eps, positions=None):
     gate = sigmoid(h @ w[p + "g"].T)                                              # [n, H]
     out = np.empty((n, H, dv))
     causal = np.tril(np.ones((n, n), dtype=bool))
+    if m.get("window"):                       # position i sees j with i - window < j <= i (not of this design; the part offers it)
+        causal &= ~np.tril(np.ones((n, n), dtype=bool), -int(m["window"]))
     for head in range(H):
         kv = head // (H // G)
         s = np.where(causal, (q[:, head] @ k[:, kv].T) * m["scale"], -np.inf)

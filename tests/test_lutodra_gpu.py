@@ -424,6 +424,46 @@ def test_attention_with_a_sink_and_a_planted_key(dtype, H, G, dk, dv, rotation, 
         rows_close(got[r][:, : H * dv], want[r][:, : H * dv], 3e-5 if dtype == "float32" else 3e-2, f"attention {r}")
 
 
+@pytest.mark.parametrize("dtype,H,G,d,window,page", [("float32", 2, 1, 16, 21, 16), ("bfloat16", 4, 2, 64, 33, 16), ("bfloat16", 2, 2, 128, 24, 32),
+                                                     ("float32", 3, 3, 8, 1, 16)])
+def test_the_part_s_window_with_a_sink(dtype, H, G, d, window, page):
+    """The part takes a window (no layer of this design has one): position i sees the last ``window`` keys.  Every
+    key leans towards the queries' direction, some more than others, so that a key more or fewer at the window's far edge
+    moves the result beyond rounding (the plain implementation with a window one off says by how much); the sink stays in
+    the denominator."""
+    from vllm_cpp_b200.config.model_spec import PartSpec
+    from vllm_cpp_b200.parts import model as _registers_every_part  # noqa: F401
+    from vllm_cpp_b200.parts.sink_attention import SinkAttention
+    rng = np.random.default_rng(window)
+    T, scale, eps = 150, 0.3, 1e-5
+    o0, o1, o2 = H * d, H * d + G * d, H * d + 2 * G * d
+    width = o2 + H
+    m = {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": scale, "rot": None, "window": window}
+    part = SinkAttention(width, H, G, d, d, scale, eps, PartSpec("none"), DT[dtype], "cuda", window=window)
+    eye, p = np.eye(width), "x."
+    gain = stored(np.full(d, (1.5 if dtype == "float32" else 1.0) / np.sqrt(scale) / d ** 0.25), "bfloat16")
+    w = {p + "q": eye[:o0], p + "k": eye[o0:o1], p + "v": eye[o1:o2], p + "g": eye[o2:], p + "o": eye[:, : H * d],
+         p + "q.norm": gain, p + "k.norm": gain, p + "sink": stored(2.0 + rng.standard_normal(H), "bfloat16")}
+    part.load_params(part_weights(w, p, dtype))
+    x = {r: rng.standard_normal((n, width)) for r, n in (("a", T), ("b", 70))}
+    direction = 2.0 * np.sign(rng.standard_normal(d))
+    for r in x:
+        for t in range(len(x[r])):                       # every key carries the direction, one in five strongly
+            for g in range(G):
+                x[r][t, o0 + g * d: o0 + (g + 1) * d] += direction * (1.0 + 1.0 * ((len(x[r]) - t) % 5))
+        for h in range(H):
+            x[r][:, h * d: (h + 1) * d] += direction
+    x = {r: stored(a, dtype) for r, a in x.items()}
+    want = {r: plain.attention_mixer(w, p, m, x[r], eps) for r in x}
+    for other in (window + 1, max(window - 1, 1)) if window > 1 else (2,):
+        off = plain.attention_mixer(w, p, dict(m, window=other), x["a"], eps)
+        assert np.abs(off - want["a"]).max() > 0.03 * np.abs(want["a"]).max()
+    steps = [[("a", 40), ("b", 3)], [("b", 60), ("a", 1)], [("a", 70), ("b", 1)]] + [[("a", 1), ("b", 1)]] * 6 + [[("a", 1)]] * 20 + [[("a", 13)]]
+    got, _ = run_mixer(part, x, steps, page=page, pages=2 * (-(-T // page)) + 2, max_len=T + page, max_seqs=3, width_out=width)
+    for r in x:
+        rows_close(got[r][:, : H * d], want[r][:, : H * d], 3e-5 if dtype == "float32" else 3e-2, f"window {r}")
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("n,width,ff,experts,top,groups,scale", [(9, 72, 40, 6, 2, (3, 2), 2.5), (150, 64, 24, 3, 3, None, 1.0),
                                                                  (33, 80, 16, 8, 3, (4, 2), 0.5), (700, 48, 20, 15, 4, (3, 1), 1.25),
