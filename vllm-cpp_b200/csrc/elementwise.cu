@@ -106,7 +106,7 @@ VCB_EXPORT int vcb_embedding(const void* table, const int* ids, float* residual,
 template <typename T>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta,
                                    const float* __restrict__ gain, T* __restrict__ out,
-                                   const int* __restrict__ row_index, int hidden, float eps) {
+                                   const int* __restrict__ row_index, int hidden, float eps, float mult) {
     __shared__ float scratch[33];
     pdl_start();
     const int o = blockIdx.x;
@@ -119,7 +119,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
     float ss = 0.0f;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
         float x = res[i];
-        if (dl) x += to_f32<T>(dl[i]);
+        if (dl) x = fmaf(mult, to_f32<T>(dl[i]), x);
         if (write_back) res[i] = x;
         ss += x * x;
     }
@@ -127,7 +127,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
     const float r = 1.0f / sqrtf(ss / (float)hidden + eps);
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
         float x = res[i];
-        if (dl && !write_back) x += to_f32<T>(dl[i]);
+        if (dl && !write_back) x = fmaf(mult, to_f32<T>(dl[i]), x);
         dst[i] = from_f32<T>((x * r) * gain[i]);
     }
 }
@@ -159,7 +159,7 @@ template <> struct Vec4<__nv_bfloat16> {
 template <typename T, int NV>
 __global__ void __launch_bounds__(NV == 8 ? 512 : 256) add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta,
                                        const float* __restrict__ gain, T* __restrict__ out,
-                                       const int* __restrict__ row_index, int hidden, float eps) {
+                                       const int* __restrict__ row_index, int hidden, float eps, float mult) {
     __shared__ float scratch[33];
     pdl_start();
     const int o = blockIdx.x;
@@ -183,7 +183,7 @@ __global__ void __launch_bounds__(NV == 8 ? 512 : 256) add_rmsnorm_vec_kernel(fl
         const int i = threadIdx.x + k * blockDim.x;
         if (i < nvec) {
             float4 v = x[k];
-            if (dl) { v.x += dv[k].x; v.y += dv[k].y; v.z += dv[k].z; v.w += dv[k].w; }
+            if (dl) { v.x = fmaf(mult, dv[k].x, v.x); v.y = fmaf(mult, dv[k].y, v.y); v.z = fmaf(mult, dv[k].z, v.z); v.w = fmaf(mult, dv[k].w, v.w); }
             if (write_back) Vec4<float>::store(res + 4 * i, v);
             ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
             x[k] = v;
@@ -205,34 +205,72 @@ __global__ void __launch_bounds__(NV == 8 ? 512 : 256) add_rmsnorm_vec_kernel(fl
 
 template <typename T>
 static void launch_add_rmsnorm(float* residual, const T* delta, const float* gain, T* out, const int* row_index,
-                               int n_rows, int hidden, float eps, cudaStream_t s) {
+                               int n_rows, int hidden, float eps, float mult, cudaStream_t s) {
     const bool aligned = (hidden % 4 == 0) && ((((uintptr_t)residual | (uintptr_t)gain) & 15) == 0) &&
                          ((((uintptr_t)delta | (uintptr_t)out) & 7) == 0);
     const int nvec = hidden / 4;
     if (aligned && nvec <= 128 * 4)
-        vcb_launch(add_rmsnorm_vec_kernel<T, 4>, n_rows, 128, 0, s, residual, delta, gain, out, row_index, hidden, eps);
+        vcb_launch(add_rmsnorm_vec_kernel<T, 4>, n_rows, 128, 0, s, residual, delta, gain, out, row_index, hidden, eps, mult);
     else if (aligned && nvec <= 256 * 4)
-        vcb_launch(add_rmsnorm_vec_kernel<T, 4>, n_rows, 256, 0, s, residual, delta, gain, out, row_index, hidden, eps);
+        vcb_launch(add_rmsnorm_vec_kernel<T, 4>, n_rows, 256, 0, s, residual, delta, gain, out, row_index, hidden, eps, mult);
     else if (aligned && nvec <= 512 * 8)        // a row and its addend in registers: 64 of them a thread at eight vectors
-        vcb_launch(add_rmsnorm_vec_kernel<T, 8>, n_rows, 512, 0, s, residual, delta, gain, out, row_index, hidden, eps);
+        vcb_launch(add_rmsnorm_vec_kernel<T, 8>, n_rows, 512, 0, s, residual, delta, gain, out, row_index, hidden, eps, mult);
     else {
         const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
-        vcb_launch(add_rmsnorm_kernel<T>, n_rows, threads, 0, s, residual, delta, gain, out, row_index, hidden, eps);
+        vcb_launch(add_rmsnorm_kernel<T>, n_rows, threads, 0, s, residual, delta, gain, out, row_index, hidden, eps, mult);
     }
+}
+
+// residual += mult * delta (one multiply-add in float; mult 1 is the plain sum), then the norm.
+VCB_EXPORT int vcb_add_rmsnorm_scaled(float* residual, const void* delta, const float* gain, void* out,
+                                      const int* row_index, int n_rows, int hidden, float eps, float mult, int dtype,
+                                      void* stream) {
+    if (n_rows <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == VCB_F32)
+        launch_add_rmsnorm<float>(residual, (const float*)delta, gain, (float*)out, row_index, n_rows, hidden, eps, mult, s);
+    else if (dtype == VCB_BF16)
+        launch_add_rmsnorm<__nv_bfloat16>(residual, (const __nv_bfloat16*)delta, gain, (__nv_bfloat16*)out,
+                                          row_index, n_rows, hidden, eps, mult, s);
+    else
+        return VCB_ERR_BAD_ARG;
+    return vcb_last_error();
 }
 
 VCB_EXPORT int vcb_add_rmsnorm(float* residual, const void* delta, const float* gain, void* out,
                                const int* row_index, int n_rows, int hidden, float eps, int dtype,
                                void* stream) {
-    if (n_rows <= 0) return 0;
+    return vcb_add_rmsnorm_scaled(residual, delta, gain, out, row_index, n_rows, hidden, eps, 1.0f, dtype, stream);
+}
+
+// ------------------------------------------------------- rows of the stream in the compute type
+// out[t, i] = x[t, i] + mult * delta[t, i] (float; delta may be null) rounded to T; out rows ldo apart.  Nothing is
+// written back: for a caller that replaces the stream right after (a product whose input is the stream itself).
+template <typename T>
+__global__ void cast_rows_kernel(const float* __restrict__ x, const T* __restrict__ delta, float mult, T* __restrict__ out,
+                                 int width, long long ldo, long long total) {
+    pdl_start();
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+        const long long t = idx / width;
+        const int i = (int)(idx - t * width);
+        float v = x[idx];
+        if (delta) v = fmaf(mult, to_f32<T>(delta[idx]), v);
+        out[t * ldo + i] = from_f32<T>(v);
+    }
+}
+
+VCB_EXPORT int vcb_cast_rows(const float* x, const void* delta, float mult, void* out, int n, int width, long long ldo, int dtype,
+                             void* stream) {
+    if (n <= 0 || width <= 0) return 0;
+    if (!x || !out || ldo < width) return VCB_ERR_BAD_ARG;
+    const long long total = (long long)n * width;
+    long long blocks = (total + 255) / 256;
+    if (blocks > (long long)vcb_sm_count() * 16) blocks = (long long)vcb_sm_count() * 16;
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == VCB_F32)
-        launch_add_rmsnorm<float>(residual, (const float*)delta, gain, (float*)out, row_index, n_rows, hidden, eps, s);
+    if (dtype == VCB_F32) vcb_launch(cast_rows_kernel<float>, (int)blocks, 256, 0, s, x, (const float*)delta, mult, (float*)out, width, ldo, total);
     else if (dtype == VCB_BF16)
-        launch_add_rmsnorm<__nv_bfloat16>(residual, (const __nv_bfloat16*)delta, gain, (__nv_bfloat16*)out,
-                                          row_index, n_rows, hidden, eps, s);
-    else
-        return VCB_ERR_BAD_ARG;
+        vcb_launch(cast_rows_kernel<__nv_bfloat16>, (int)blocks, 256, 0, s, x, (const __nv_bfloat16*)delta, mult, (__nv_bfloat16*)out, width, ldo, total);
+    else return VCB_ERR_BAD_ARG;
     return vcb_last_error();
 }
 
@@ -319,6 +357,86 @@ VCB_EXPORT int vcb_silu_mul(const void* gu, void* out, int n_tokens, int inter, 
         vcb_launch(silu_mul_kernel<float>, grid, threads, 0, s, (const float*)gu, (float*)out, inter);
     else if (dtype == VCB_BF16)
         vcb_launch(silu_mul_kernel<__nv_bfloat16>, grid, threads, 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter);
+    else
+        return VCB_ERR_BAD_ARG;
+    return vcb_last_error();
+}
+
+// The clamped gated activation, with the projections' biases when they have some:
+//   g = min(gu[t, i] + bias[i], limit),  u = clamp(gu[t, inter + i] + bias[inter + i], -limit, limit)
+//   out[t, i] = g * sigmoid(alpha * g) * (u + up_shift)
+// (bias: float [2 * inter] or null).  The sums, the sigmoid and the products are float; expf and a true division.
+template <typename T>
+__global__ void clamped_swish_mul_kernel(const T* __restrict__ gu, const float* __restrict__ bias, T* __restrict__ out,
+                                         int inter, float limit, float alpha, float up_shift) {
+    pdl_start();
+    const int t = blockIdx.y;
+    const T* g = gu + (size_t)t * 2 * inter;
+    const T* u = g + inter;
+    T* o = out + (size_t)t * inter;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < inter; i += gridDim.x * blockDim.x) {
+        float a = to_f32<T>(g[i]), b = to_f32<T>(u[i]);
+        if (bias) { a += bias[i]; b += bias[inter + i]; }
+        a = fminf(a, limit);
+        b = fminf(fmaxf(b, -limit), limit);
+        o[i] = from_f32<T>(a * (1.0f / (1.0f + expf(-alpha * a))) * (b + up_shift));
+    }
+}
+
+// bfloat16 rows of a multiple of 8 columns: 16 bytes of gate and of up a thread.
+__global__ void clamped_swish_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, const float* __restrict__ bias,
+                                                __nv_bfloat16* __restrict__ out, int inter, long long n_vec, float limit,
+                                                float alpha, float up_shift) {
+    pdl_start();
+    const long long vpr = inter >> 3;
+    for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < n_vec; v += (long long)gridDim.x * blockDim.x) {
+        const long long t = v / vpr;
+        const int i = (int)(v - t * vpr) << 3;
+        const __nv_bfloat16* row = gu + (size_t)t * 2 * inter;
+        const uint4 g4 = *reinterpret_cast<const uint4*>(row + i), u4 = *reinterpret_cast<const uint4*>(row + inter + i);
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
+        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
+        uint4 o4;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            float2 a = __bfloat1622float2(g2[e]), b = __bfloat1622float2(u2[e]);
+            if (bias) {
+                a.x += bias[i + 2 * e]; a.y += bias[i + 2 * e + 1];
+                b.x += bias[inter + i + 2 * e]; b.y += bias[inter + i + 2 * e + 1];
+            }
+            a.x = fminf(a.x, limit); a.y = fminf(a.y, limit);
+            b.x = fminf(fmaxf(b.x, -limit), limit); b.y = fminf(fmaxf(b.y, -limit), limit);
+            o2[e] = __floats2bfloat162_rn(a.x * (1.0f / (1.0f + expf(-alpha * a.x))) * (b.x + up_shift),
+                                          a.y * (1.0f / (1.0f + expf(-alpha * a.y))) * (b.y + up_shift));
+        }
+        *reinterpret_cast<uint4*>(out + (size_t)t * inter + i) = o4;
+    }
+}
+
+VCB_EXPORT int vcb_clamped_swish_mul(const void* gu, const float* bias, void* out, int n_tokens, int inter, float limit,
+                                     float alpha, float up_shift, int dtype, void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (inter <= 0 || !(limit > 0.0f)) return VCB_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == VCB_BF16 && inter % 8 == 0 && ((((uintptr_t)gu | (uintptr_t)out) & 15) == 0)) {
+        const long long n_vec = (long long)n_tokens * (inter >> 3);
+        long long blocks = (n_vec + 255) / 256;
+        if (blocks > (long long)vcb_sm_count() * 16) blocks = (long long)vcb_sm_count() * 16;
+        vcb_launch(clamped_swish_mul_bf16x8_kernel, (int)blocks, 256, 0, s, (const __nv_bfloat16*)gu, bias, (__nv_bfloat16*)out,
+                   inter, n_vec, limit, alpha, up_shift);
+        return vcb_last_error();
+    }
+    const int threads = 256;
+    int bx = (inter + threads - 1) / threads;
+    if (bx > 64) bx = 64;
+    if (n_tokens > 65535) return VCB_ERR_UNSUPPORTED;
+    dim3 grid(bx, n_tokens);
+    if (dtype == VCB_F32)
+        vcb_launch(clamped_swish_mul_kernel<float>, grid, threads, 0, s, (const float*)gu, bias, (float*)out, inter, limit, alpha, up_shift);
+    else if (dtype == VCB_BF16)
+        vcb_launch(clamped_swish_mul_kernel<__nv_bfloat16>, grid, threads, 0, s, (const __nv_bfloat16*)gu, bias, (__nv_bfloat16*)out,
+                   inter, limit, alpha, up_shift);
     else
         return VCB_ERR_BAD_ARG;
     return vcb_last_error();

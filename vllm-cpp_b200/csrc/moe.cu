@@ -92,8 +92,8 @@ struct RouteRule {
 };
 
 __global__ void __launch_bounds__(128)
-moe_router_select_kernel(const float* __restrict__ logits, const float* __restrict__ correction, int* __restrict__ ids,
-                         float* __restrict__ wts, int n_tokens, int n_out, int top, RouteRule rule) {
+moe_router_select_kernel(const float* __restrict__ logits, const float* __restrict__ logit_bias, const float* __restrict__ correction,
+                         int* __restrict__ ids, float* __restrict__ wts, int n_tokens, int n_out, int top, RouteRule rule) {
     extern __shared__ float sm[];
     pdl_start();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -102,17 +102,18 @@ moe_router_select_kernel(const float* __restrict__ logits, const float* __restri
     float* score = sm + (size_t)warp * (2 * n_out + rule.n_groups);      // [n_out] scores
     float* choice = score + n_out;                     // [n_out] score + correction; -inf once taken or shut out
     float* gscore = choice + n_out;                    // [n_groups]
-    const float* z = logits + (size_t)t * n_out;
+    const float* zr = logits + (size_t)t * n_out;
+    auto z = [&](int e) { return logit_bias ? zr[e] + logit_bias[e] : zr[e]; };      // the router's bias joins the logits themselves (float)
     if (rule.score_fn == 0) {
         float m = -INFINITY;
-        for (int e = lane; e < n_out; e += 32) m = fmaxf(m, z[e]);
+        for (int e = lane; e < n_out; e += 32) m = fmaxf(m, z(e));
         m = warp_max(m);
         float sum = 0.0f;
-        for (int e = lane; e < n_out; e += 32) { const float p = expf(z[e] - m); score[e] = p; sum += p; }
+        for (int e = lane; e < n_out; e += 32) { const float p = expf(z(e) - m); score[e] = p; sum += p; }
         sum = warp_sum(sum);
         for (int e = lane; e < n_out; e += 32) score[e] = score[e] / sum;
     } else {
-        for (int e = lane; e < n_out; e += 32) score[e] = 1.0f / (1.0f + expf(-z[e]));
+        for (int e = lane; e < n_out; e += 32) score[e] = 1.0f / (1.0f + expf(-z(e)));
     }
     for (int e = lane; e < n_out; e += 32) choice[e] = score[e] + (correction ? correction[e] : 0.0f);
     __syncwarp();
@@ -182,10 +183,11 @@ moe_router_select_kernel(const float* __restrict__ logits, const float* __restri
 }
 
 // logits: float scratch [n_tokens, n_out].
-VCB_EXPORT int vcb_moe_router_ruled(const void* h, long long ldh, const float* wr, const float* correction, float* logits, int* ids,
-                                    float* wts, int n_tokens, int width, int n_out, int top, int score_fn, int n_groups,
-                                    int keep_groups, int group_top, int normalize, float sum_eps, float scale, int dtype,
-                                    void* stream) {
+// logit_bias: float [n_out] added to the logits before the scores are made, or null.
+VCB_EXPORT int vcb_moe_router_biased(const void* h, long long ldh, const float* wr, const float* logit_bias, const float* correction,
+                                     float* logits, int* ids, float* wts, int n_tokens, int width, int n_out, int top, int score_fn,
+                                     int n_groups, int keep_groups, int group_top, int normalize, float sum_eps, float scale,
+                                     int dtype, void* stream) {
     if (n_tokens <= 0) return 0;
     if (!h || !wr || !logits || !ids || !wts || width <= 0 || n_out <= 0 || top <= 0 || top > n_out) return VCB_ERR_BAD_ARG;
     if (n_groups <= 0 || n_out % n_groups || keep_groups <= 0 || keep_groups > n_groups || group_top <= 0 || group_top > 4 ||
@@ -200,8 +202,16 @@ VCB_EXPORT int vcb_moe_router_ruled(const void* h, long long ldh, const float* w
         vcb_launch(moe_router_logits_kernel<__nv_bfloat16>, grid, 256, 0, s, (const __nv_bfloat16*)h, ldh, wr, logits, n_tokens, width, n_out);
     else return VCB_ERR_BAD_ARG;
     RouteRule rule{score_fn, n_groups, keep_groups, group_top, normalize, sum_eps, scale};
-    vcb_launch(moe_router_select_kernel, (n_tokens + 3) / 4, 128, smem, s, (const float*)logits, correction, ids, wts, n_tokens, n_out, top, rule);
+    vcb_launch(moe_router_select_kernel, (n_tokens + 3) / 4, 128, smem, s, (const float*)logits, logit_bias, correction, ids, wts, n_tokens, n_out, top, rule);
     return vcb_last_error();
+}
+
+VCB_EXPORT int vcb_moe_router_ruled(const void* h, long long ldh, const float* wr, const float* correction, float* logits, int* ids,
+                                    float* wts, int n_tokens, int width, int n_out, int top, int score_fn, int n_groups,
+                                    int keep_groups, int group_top, int normalize, float sum_eps, float scale, int dtype,
+                                    void* stream) {
+    return vcb_moe_router_biased(h, ldh, wr, nullptr, correction, logits, ids, wts, n_tokens, width, n_out, top, score_fn, n_groups,
+                                 keep_groups, group_top, normalize, sum_eps, scale, dtype, stream);
 }
 
 // Softmax scores, no groups, the plain scores as weights.
@@ -505,11 +515,12 @@ VCB_EXPORT int vcb_moe_expert_gemm(const void* A, long long lda, const void* W, 
 // ------------------------------------------------------------------------------------------ combine
 template <typename T>
 __global__ void moe_combine_kernel(const float* __restrict__ y, const T* __restrict__ h, long long ldh, const int* __restrict__ pos,
-                                   const float* __restrict__ wts, T* __restrict__ out, int width, int top) {
+                                   const float* __restrict__ wts, T* __restrict__ out, int width, int top,
+                                   const T* __restrict__ add, long long lda) {
     pdl_start();
     const int t = blockIdx.x;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        float acc = 0.0f;
+        float acc = add ? to_f32<T>(add[(size_t)t * lda + i]) : 0.0f;      // what every token takes beside its choices (a shared expert)
         for (int k = 0; k < top; ++k) {
             const int p = pos[(size_t)t * top + k];
             const float w = wts[(size_t)t * top + k];
@@ -519,16 +530,21 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const T* __restr
     }
 }
 
-VCB_EXPORT int vcb_moe_combine(const float* y, const void* h, long long ldh, const int* pos, const float* wts, void* out,
-                               int n_tokens, int width, int top, int dtype, void* stream) {
+VCB_EXPORT int vcb_moe_combine_add(const float* y, const void* h, long long ldh, const int* pos, const float* wts, void* out,
+                                   int n_tokens, int width, int top, const void* add, long long lda, int dtype, void* stream) {
     if (n_tokens <= 0) return 0;
     if (!y || !h || !pos || !wts || !out || width <= 0 || top <= 0) return VCB_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = width >= 1024 ? 256 : 128;
-    if (dtype == VCB_F32) vcb_launch(moe_combine_kernel<float>, n_tokens, threads, 0, s, y, (const float*)h, ldh, pos, wts, (float*)out, width, top);
+    if (dtype == VCB_F32) vcb_launch(moe_combine_kernel<float>, n_tokens, threads, 0, s, y, (const float*)h, ldh, pos, wts, (float*)out, width, top, (const float*)add, lda);
     else if (dtype == VCB_BF16)
         vcb_launch(moe_combine_kernel<__nv_bfloat16>, n_tokens, threads, 0, s, y, (const __nv_bfloat16*)h, ldh, pos, wts,
-                   (__nv_bfloat16*)out, width, top);
+                   (__nv_bfloat16*)out, width, top, (const __nv_bfloat16*)add, lda);
     else return VCB_ERR_BAD_ARG;
     return vcb_last_error();
+}
+
+VCB_EXPORT int vcb_moe_combine(const float* y, const void* h, long long ldh, const int* pos, const float* wts, void* out,
+                               int n_tokens, int width, int top, int dtype, void* stream) {
+    return vcb_moe_combine_add(y, h, ldh, pos, wts, out, n_tokens, width, top, nullptr, 0, dtype, stream);
 }

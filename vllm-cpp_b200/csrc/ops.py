@@ -52,8 +52,16 @@ _SIGNATURES = {
     "vcb_token_shift": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
     "vcb_gated_norm_residual": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _F, _F, _I, _P],
     "vcb_latent_cache_write": [_P, _I, _P, _P, _P, _P, _I, _P, ctypes.c_longlong, _I, _I, _I, _F, _I, _P, _I, _P],
-    "vcb_headwise_linear": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
-    "vcb_sigmoid_gate": [_P, _P, _I, _I, _I, _I, _I, _P],
+    "vcb_headwise_linear": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "vcb_sigmoid_gate": [_P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "vcb_rows_rmsnorm": [_P, _I, _P, _P, _I, _I, _I, _F, _I, _P],
+    "vcb_latent_rope_cache_write": [_P, _I, _P, _P, _I, _I, _I, _I, _P, _I, _I, _P, _P, _P, _I, _P, _L, _I, _I, _I, _F, _I, _I, _P, _I, _P],
+    "vcb_cast_rows": [_P, _P, _F, _P, _I, _I, _L, _I, _P],
+    "vcb_add_rmsnorm_scaled": [_P, _P, _P, _P, _P, _I, _I, _F, _F, _I, _P],
+    "vcb_clamped_swish_mul": [_P, _P, _P, _I, _I, _F, _F, _F, _I, _P],
+    "vcb_moe_router_biased": [_P, _L, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P],
+    "vcb_moe_combine_add": [_P, _P, _L, _P, _P, _P, _I, _I, _I, _P, _L, _I, _P],
+    "vcb_attention_talking": [_P, _P, _P, _P, _L, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _I, _P],
     "vcb_attention_decode_mma_shaped": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _I, _F, _P, _I,
                                         _P, _P, _L, _I, _P],
     "vcb_attention_prefill_tc_shaped": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _F, _P, _I, _P, _P, _L, _I, _P],
@@ -188,8 +196,8 @@ def embedding(table: torch.Tensor, ids: torch.Tensor, residual: torch.Tensor, sc
 
 
 def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], gain: torch.Tensor,
-                out: torch.Tensor, eps: float, row_index: Optional[torch.Tensor] = None) -> None:
-    """out = rmsnorm(residual (+ delta)) * gain; the sum is written back to residual unless rows are gathered."""
+                out: torch.Tensor, eps: float, row_index: Optional[torch.Tensor] = None, mult: float = 1.0) -> None:
+    """out = rmsnorm(residual (+ mult * delta)) * gain; the sum is written back to residual unless rows are gathered."""
     hidden = residual.shape[1]
     n_rows = out.shape[0]
     _need(out.shape[1] == hidden and gain.numel() == hidden, "add_rmsnorm: widths differ")
@@ -199,11 +207,11 @@ def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], gain: tor
         _need(n_rows == residual.shape[0], "add_rmsnorm: one output row per residual row")
     else:
         _need(row_index.numel() == n_rows, "add_rmsnorm: one row index per output row")
-    _check(lib().vcb_add_rmsnorm(_dev(residual, "residual", torch.float32),
-                                 None if delta is None else _dev(delta, "delta"),
-                                 _dev(gain, "gain", torch.float32), _dev(out, "out"),
-                                 None if row_index is None else _dev(row_index, "row_index", torch.int32),
-                                 n_rows, hidden, float(eps), dtype_code(out.dtype), _stream()), "add_rmsnorm")
+    _check(lib().vcb_add_rmsnorm_scaled(_dev(residual, "residual", torch.float32),
+                                        None if delta is None else _dev(delta, "delta"),
+                                        _dev(gain, "gain", torch.float32), _dev(out, "out"),
+                                        None if row_index is None else _dev(row_index, "row_index", torch.int32),
+                                        n_rows, hidden, float(eps), float(mult), dtype_code(out.dtype), _stream()), "add_rmsnorm")
 
 
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
@@ -212,6 +220,29 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
     _need(gate_up.shape == (n, 2 * inter) and gate_up.dtype == out.dtype, "silu_mul: gate_up must be [n, 2*inter]")
     _check(lib().vcb_silu_mul(_dev(gate_up, "gate_up"), _dev(out, "out"), n, inter,
                               dtype_code(out.dtype), _stream()), "silu_mul")
+
+
+def cast_rows(x: torch.Tensor, delta: Optional[torch.Tensor], mult: float, out: torch.Tensor) -> None:
+    """out = x + mult * delta (float; ``delta`` None: x itself) rounded to out's type; x float32 [n, width] contiguous,
+    delta contiguous of out's type, out rows may be strided.  x is left as it is."""
+    n, width = x.shape
+    _need(out.shape == x.shape and out.stride(1) == 1 and out.is_cuda, "cast_rows: out like x, unit inner stride")
+    _need(delta is None or (delta.shape == x.shape and delta.dtype == out.dtype), "cast_rows: delta like x, of out's type")
+    _check(lib().vcb_cast_rows(_dev(x, "x", torch.float32), None if delta is None else _dev(delta, "delta"), float(mult),
+                               out.data_ptr(), n, width, out.stride(0), dtype_code(out.dtype), _stream()), "cast_rows")
+
+
+def clamped_swish_mul(gate_up: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, *, limit: float, alpha: float,
+                      up_shift: float = 1.0) -> None:
+    """out[t, i] = g * sigmoid(alpha * g) * (u + up_shift) with g = min(gate_up[t, i] + bias[i], limit) and
+    u = clamp(gate_up[t, inter + i] + bias[inter + i], -limit, limit); ``bias`` float32 [2 * inter] or None."""
+    n, inter = out.shape
+    _need(gate_up.shape == (n, 2 * inter) and gate_up.dtype == out.dtype, "clamped_swish_mul: gate_up must be [n, 2*inter]")
+    _need(bias is None or bias.numel() == 2 * inter, "clamped_swish_mul: one bias value per gate and up feature")
+    _need(limit > 0, "clamped_swish_mul: limit must be positive")
+    _check(lib().vcb_clamped_swish_mul(_dev(gate_up, "gate_up"), None if bias is None else _dev(bias, "bias", torch.float32),
+                                       _dev(out, "out"), n, inter, float(limit), float(alpha), float(up_shift),
+                                       dtype_code(out.dtype), _stream()), "clamped_swish_mul")
 
 
 def add_bias(x: torch.Tensor, bias: torch.Tensor) -> None:
@@ -1113,13 +1144,15 @@ ROUTER_GROUP_TOP_MAX = 4
 
 def moe_router(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], ids: torch.Tensor,
                weights: torch.Tensor, logits: torch.Tensor, *, score: str = "softmax", groups: int = 1, keep_groups: int = 1,
-               group_top: int = 1, normalize: bool = False, sum_eps: float = 0.0, scale: float = 1.0) -> None:
+               group_top: int = 1, normalize: bool = False, sum_eps: float = 0.0, scale: float = 1.0,
+               logit_bias: Optional[torch.Tensor] = None) -> None:
     """For every row of h: scores in float32 from the logits w_router h, by softmax over all router outputs or by a
     sigmoid of each (``score``); ids [n, top] = the outputs with the largest score + correction (the lower index wins
     among equals), with ``groups`` > ``keep_groups`` only among the ``keep_groups`` best of ``groups`` equal groups of
     neighbouring outputs (a group's score: the sum of its ``group_top`` largest); weights [n, top] = their plain scores,
-    with ``normalize`` divided by (their sum + ``sum_eps``), times ``scale``.  ``logits``: float32 scratch
-    [n, router outputs].  Two kernels (csrc/moe.cu)."""
+    with ``normalize`` divided by (their sum + ``sum_eps``), times ``scale``.  ``logit_bias`` (float32 [router outputs]) joins
+    the logits before the scores are made.  Softmax scores of the chosen, normalized, are the softmax over the chosen
+    logits alone.  ``logits``: float32 scratch [n, router outputs].  Two kernels (csrc/moe.cu)."""
     _need(score in ROUTER_SCORES, f"moe_router: score is one of {sorted(ROUTER_SCORES)}")
     _need(groups >= 1 and w_router.shape[0] % groups == 0 and 1 <= keep_groups <= groups and 1 <= group_top <= ROUTER_GROUP_TOP_MAX,
           "moe_router: equal groups, some of them kept, a group's score from at most four outputs")
@@ -1129,8 +1162,10 @@ def moe_router(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[tor
     top = ids.shape[1]
     _need(w_router.shape[1] == width and ids.shape == (n, top) and weights.shape == (n, top), "moe_router: shapes")
     _need(correction is None or correction.numel() == w_router.shape[0], "moe_router: one correction per router output")
+    _need(logit_bias is None or logit_bias.numel() == w_router.shape[0], "moe_router: one bias per router output")
     _need(logits.dtype == torch.float32 and logits.is_contiguous() and logits.numel() >= n * w_router.shape[0], "moe_router: logits scratch")
-    _check(lib().vcb_moe_router_ruled(h.data_ptr(), h.stride(0), _dev(w_router, "w_router", torch.float32),
+    _check(lib().vcb_moe_router_biased(h.data_ptr(), h.stride(0), _dev(w_router, "w_router", torch.float32),
+                                      None if logit_bias is None else _dev(logit_bias, "logit_bias", torch.float32),
                                       None if correction is None else _dev(correction, "correction", torch.float32),
                                       logits.data_ptr(), _dev(ids, "ids", torch.int32), _dev(weights, "weights", torch.float32), n, width,
                                       w_router.shape[0], top, ROUTER_SCORES[score], groups, keep_groups, group_top,
@@ -1168,14 +1203,20 @@ def moe_expert_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, sorted_
                                      dtype_code(a.dtype), _stream()), "moe_expert_gemm")
 
 
-def moe_combine(y: torch.Tensor, h: torch.Tensor, pos: torch.Tensor, weights: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t] = sum_k weights[t, k] * (y[pos[t, k]] if pos[t, k] >= 0 else h[t]); y float32 [pairs, width]."""
+def moe_combine(y: torch.Tensor, h: torch.Tensor, pos: torch.Tensor, weights: torch.Tensor, out: torch.Tensor,
+                add: Optional[torch.Tensor] = None) -> None:
+    """out[t] = sum_k weights[t, k] * (y[pos[t, k]] if pos[t, k] >= 0 else h[t]) (+ add[t]: what every token takes beside
+    its choices, rows of out's type); y float32 [pairs, width]."""
     n, width = out.shape
     _rows(h, "h", out.dtype)
     _need(y.dtype == torch.float32 and y.is_contiguous() and y.shape[1] == width and h.shape == out.shape, "moe_combine: shapes")
-    _check(lib().vcb_moe_combine(y.data_ptr(), h.data_ptr(), h.stride(0), _dev(pos, "pos", torch.int32),
-                                 _dev(weights, "weights", torch.float32), _dev(out, "out"), n, width, weights.shape[1],
-                                 dtype_code(out.dtype), _stream()), "moe_combine")
+    if add is not None:
+        _rows(add, "add", out.dtype)
+        _need(add.shape == out.shape, "moe_combine: add like out")
+    _check(lib().vcb_moe_combine_add(y.data_ptr(), h.data_ptr(), h.stride(0), _dev(pos, "pos", torch.int32),
+                                     _dev(weights, "weights", torch.float32), _dev(out, "out"), n, width, weights.shape[1],
+                                     None if add is None else add.data_ptr(), 0 if add is None else add.stride(0),
+                                     dtype_code(out.dtype), _stream()), "moe_combine")
 
 
 # ------------------------------------------------- a residual stream of several copies, read through a layer norm
@@ -1358,37 +1399,104 @@ def latent_cache_write(raw: torch.Tensor, gain: torch.Tensor, positions, req_of_
 HEADWISE_LIBRARY_TOKENS = 128      # bfloat16 portions longer than this run the library's batched product
 
 
-def headwise_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor] = None) -> None:
+def headwise_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor] = None,
+                    gate_per_head: bool = False) -> None:
     """out[t, h, :] = x[t, h, :] @ w[h]^T for every head: x [n, heads * K] (rows may be strided), w [heads, N, K],
-    out [n, heads * N]; with ``gate`` ([n, heads * N], rows may be strided) out *= sigmoid(gate).  float32 and
-    short bfloat16 steps: this library's kernel; long bfloat16 portions: the library's batched product, then
-    the gate as a kernel."""
+    out [n, heads * N]; with ``gate`` ([n, heads * N], or with ``gate_per_head`` [n, heads]: one number per head; rows
+    may be strided) out *= sigmoid(gate).  float32 and short bfloat16 steps: this library's kernel; long bfloat16
+    portions: the library's batched product, then the gate as a kernel."""
     heads, N, K = w.shape
     n = x.shape[0]
     _need(x.shape == (n, heads * K) and out.shape == (n, heads * N) and x.stride(1) == 1 and out.stride(1) == 1,
           "headwise_linear: x [n, heads * K], out [n, heads * N]")
     _need(w.is_contiguous() and x.dtype == w.dtype == out.dtype, "headwise_linear: one type, contiguous weights")
     if gate is not None:
-        _need(gate.shape == out.shape and gate.stride(1) == 1 and gate.dtype == out.dtype, "headwise_linear: gate like out")
+        _need(gate.shape == ((n, heads) if gate_per_head else out.shape) and gate.stride(1) == 1 and gate.dtype == out.dtype,
+              "headwise_linear: gate like out, or one column per head")
     if x.dtype == torch.bfloat16 and n > HEADWISE_LIBRARY_TOKENS:
         xh = x.unflatten(1, (heads, K)).transpose(0, 1)             # [heads, n, K]
         oh = out.unflatten(1, (heads, N)).transpose(0, 1)           # [heads, n, N]
         torch.bmm(xh, w.transpose(1, 2), out=oh)                    # the library writes the strided rows itself
         if gate is not None:
             _check(lib().vcb_sigmoid_gate(out.data_ptr(), gate.data_ptr(), n, heads * N, out.stride(0), gate.stride(0),
-                                          dtype_code(out.dtype), _stream()), "sigmoid_gate")
+                                          N if gate_per_head else 1, dtype_code(out.dtype), _stream()), "sigmoid_gate")
         return
     _check(lib().vcb_headwise_linear(x.data_ptr(), w.data_ptr(), out.data_ptr(), None if gate is None else gate.data_ptr(),
                                      n, heads, N, K, x.stride(0), out.stride(0), 0 if gate is None else gate.stride(0),
-                                     dtype_code(x.dtype), _stream()), "headwise_linear")
+                                     1 if gate_per_head else 0, dtype_code(x.dtype), _stream()), "headwise_linear")
 
 
 def sigmoid_gate(out: torch.Tensor, gate: torch.Tensor) -> None:
     """out *= sigmoid(gate) in place; rows of both may be strided."""
     n, cols = out.shape
     _need(gate.shape == out.shape and gate.dtype == out.dtype and out.stride(1) == 1 and gate.stride(1) == 1, "sigmoid_gate: gate like out")
-    _check(lib().vcb_sigmoid_gate(out.data_ptr(), gate.data_ptr(), n, cols, out.stride(0), gate.stride(0),
+    _check(lib().vcb_sigmoid_gate(out.data_ptr(), gate.data_ptr(), n, cols, out.stride(0), gate.stride(0), 1,
                                   dtype_code(out.dtype), _stream()), "sigmoid_gate")
+
+
+def rows_rmsnorm(x: torch.Tensor, gain: torch.Tensor, out: torch.Tensor, eps: float) -> None:
+    """out[t] = x[t] / sqrt(mean(x[t]^2) + eps) * gain for rows of the activations' type (both may be strided), float
+    statistics: the norm of a low-rank row between two products."""
+    n, width = x.shape
+    _need(out.shape == x.shape and out.dtype == x.dtype and x.stride(1) == 1 and out.stride(1) == 1 and x.is_cuda, "rows_rmsnorm: rows of one type")
+    _need(gain.numel() == width, "rows_rmsnorm: one gain per coordinate")
+    _check(lib().vcb_rows_rmsnorm(x.data_ptr(), x.stride(0), _dev(gain, "gain", torch.float32), out.data_ptr(), out.stride(0), n, width,
+                                  float(eps), dtype_code(x.dtype), _stream()), "rows_rmsnorm")
+
+
+def latent_rope_cache_write(raw: torch.Tensor, gain: torch.Tensor, q: Optional[torch.Tensor], inv_freq: torch.Tensor, positions,
+                            req_of_token, block_table, cache: torch.Tensor, *, rank: int, num_heads: int, q_stride: int, q_off: int,
+                            pairing: int, page_size: int, eps: float, write_kv: bool = True) -> None:
+    """``raw`` [n, rank + rot] (rows may be strided): the latent's columns, RMS-normed with ``gain``, and the ``rot`` =
+    2 * len(inv_freq) columns of a key part that all heads share, turned by the token's position (pair j: coordinates
+    (2j, 2j + 1) with ``pairing`` 1, (j, j + rot / 2) with 0; angle position * inv_freq[j] in float32), go into the token's
+    slot of a one-plane cache [pages, page_size * (rank + rot)] (kv_pos layout).  ``q`` [n, heads * q_stride] is turned in
+    place on the ``rot`` columns that start at ``q_off`` inside every head."""
+    n = raw.shape[0]
+    rot = 2 * inv_freq.numel()
+    _need(raw.shape[1] == rank + rot and raw.stride(1) == 1 and raw.is_cuda, "latent_rope_cache_write: raw [n, rank + rot]")
+    _need(cache.dtype == raw.dtype and cache.is_contiguous() and cache.numel() == cache.shape[0] * page_size * (rank + rot),
+          "latent_rope_cache_write: a one-plane cache of the activations' type with rows of rank + rot")
+    _need(gain.numel() == rank, "latent_rope_cache_write: one gain per latent coordinate")
+    if q is not None:
+        _need(q.dtype == raw.dtype and q.shape == (n, num_heads * q_stride) and q.stride(1) == 1 and q_off + rot <= q_stride,
+              "latent_rope_cache_write: q [n, heads * q_stride] with the rotated part inside a head")
+    _check(lib().vcb_latent_rope_cache_write(
+        raw.data_ptr(), raw.stride(0), _dev(gain, "gain", torch.float32), None if q is None else q.data_ptr(),
+        0 if q is None else q.stride(0), num_heads, q_stride, q_off, _dev(inv_freq, "inv_freq", torch.float32), rot, int(pairing),
+        _dev(positions, "positions", torch.int32), _dev(req_of_token, "req_of_token", torch.int32),
+        _dev(block_table, "block_table", torch.int32), block_table.shape[1], cache.data_ptr(), page_size * (rank + rot), n, rank,
+        page_size, float(eps), cache.shape[0], 1 if write_kv else 0, status_tensor(raw.device).data_ptr(), dtype_code(raw.dtype),
+        _stream()), "latent_rope_cache_write")
+
+
+TALKING_MAX_HEADS = 32
+
+
+def attention_talking(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor], positions,
+                      req_of_token, block_table, mix: torch.Tensor, slope: Optional[torch.Tensor], *, num_heads: int,
+                      num_kv_heads: int, head_dim: int, v_head_dim: int, row: int, page_size: int, window: int, scale: float) -> None:
+    """Paged attention whose heads' scores are mixed before the softmax:  raw_g = scale * q_g . k - slope[g] * distance,
+    s_h = sum_g mix[h, g] raw_g, softmax over the keys the window leaves, values of ``v_head_dim``, and out *= sigmoid(gate)
+    when a gate is given ([n, heads * v_head_dim] rows).  ``mix`` float32 [heads, heads], ``slope`` float32 [heads] or None.
+    The plain kernel: a CTA per token, a warp per head (at most 32 heads)."""
+    n = q.shape[0]
+    _need(q.shape == (n, num_heads * head_dim) and out.shape == (n, num_heads * v_head_dim) and out.dtype == q.dtype
+          and cache.dtype == q.dtype, "attention_talking: shapes or types")
+    _need(num_heads <= TALKING_MAX_HEADS, f"attention_talking: at most {TALKING_MAX_HEADS} heads")
+    _need(v_head_dim <= 256 and head_dim <= 1024, "attention_talking: head sizes up to 1024 (keys) and 256 (values)")
+    _need(mix.shape == (num_heads, num_heads) and mix.is_contiguous(), "attention_talking: mix [heads, heads]")
+    _need(slope is None or slope.numel() == num_heads, "attention_talking: one slope per head")
+    if gate is not None:
+        _rows(gate, "gate", q.dtype)
+        _need(gate.shape == out.shape, "attention_talking: gate like out")
+    _check(lib().vcb_attention_talking(
+        _dev(q, "q"), _dev(cache, "cache"), _dev(out, "out"), None if gate is None else gate.data_ptr(),
+        0 if gate is None else gate.stride(0), _dev(positions, "positions", torch.int32),
+        _dev(req_of_token, "req_of_token", torch.int32), _dev(block_table, "block_table", torch.int32), block_table.shape[1],
+        _dev(mix, "mix", torch.float32), None if slope is None else _dev(slope, "slope", torch.float32), n, num_heads, num_kv_heads,
+        head_dim, v_head_dim, row, page_size, window, float(scale), cache.shape[0], status_tensor(q.device).data_ptr(),
+        dtype_code(q.dtype), _stream()), "attention_talking")
 
 
 def random_normal(out: torch.Tensor, key: int, mean: float, std: float, first: int = 0) -> None:

@@ -1,2 +1,2 @@
 """Architectures known to the registry."""
-from . import lutodra, qwen2, retodra, rolesun  # noqa: F401
+from . import gipinex, lutodra, qwen2, retodra, rolesun  # noqa: F401

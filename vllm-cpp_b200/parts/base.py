@@ -245,8 +245,9 @@ class PositionEncoding(Part):
 
 class Norm(Part):
     def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], out: torch.Tensor,
-                row_index: Optional[torch.Tensor] = None) -> None:
-        """residual += delta (float32, in place, unless rows are gathered); out = norm(residual)."""
+                row_index: Optional[torch.Tensor] = None, mult: float = 1.0) -> None:
+        """residual += mult * delta (float32, in place, unless rows are gathered); out = norm(residual).  A norm that
+        cannot scale the addition raises for ``mult`` other than 1."""
         raise NotImplementedError
 
     def add_normed(self, y: torch.Tensor, gate: Optional[torch.Tensor], gate_bias: Optional[torch.Tensor],
@@ -328,6 +329,19 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class ScaledAddition:
+    """A value of ``pending`` (see Block.forward): ``delta`` holds an addition to ``residual`` that has not been made yet and
+    joins it times ``mult`` (a design whose residual branches carry a constant factor).  True is the same with factor 1."""
+
+    def __init__(self, mult: float):
+        self.mult = float(mult)
+
+
+def pending_mult(pending) -> float:
+    """The factor with which a pending addition joins the residual stream."""
+    return pending.mult if isinstance(pending, ScaledAddition) else 1.0
+
+
 class NormedInput:
     """A value of ``pending`` (see Block.forward): ``delta`` already holds the next block's input, normed by the norm
     that block starts with.  Only handed to a block whose ``accepts_normed`` named that norm."""
@@ -398,7 +412,7 @@ class Block:
                 cache, writes_cache: bool, ws: Workspace, next_block: "Optional[Block]" = None,
                 carry: Optional[torch.Tensor] = None, state: Optional[StateView] = None):
         """Runs the layer.  ``pending`` says what ``delta`` holds: False nothing, True an addition to
-        ``residual`` that has not been made yet, an ops.RowScale the pre-normed input (see
+        ``residual`` that has not been made yet (a ScaledAddition: one that joins times a constant), an ops.RowScale the pre-normed input (see
         accepts_prenormed; only given to a block that accepts it).  ``next_block`` runs after this
         one (None: the model's final norm does); ``carry`` is float32 scratch
         [2, ops.sumsq_parts(hidden), n_tokens] that lives for the whole step; ``state`` the view of the

@@ -1,7 +1,8 @@
 """Arrangements of a layer's parts.
 
-"prenorm":  x += mixer(norm_a(x));  x += feed_forward(norm_b(x))
-(src/model/qwen.cpp:300-318).  Each addition is carried as a pending ``delta``
+"prenorm":  x += m * mixer(norm_a(x));  x += m * feed_forward(norm_b(x))
+(src/model/qwen.cpp:300-318, where m = 1; ``residual_mult`` in the arrangement's
+constants gives another m).  Each addition is carried as a pending ``delta``
 and performed, in float, inside the norm kernel that reads the sum next.
 
 Where the parts on both sides of a norm say they can (``fuses_norm``) and the norm can be
@@ -16,13 +17,27 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
-from .base import Block, NormedInput, register_block, workspace_piece
+from .base import Block, NormedInput, ScaledAddition, pending_mult, register_block, workspace_piece
 from .mlp import NoFeedForward
 
 
 @register_block("prenorm")
 class PreNormBlock(Block):
+    """``residual_mult`` (the arrangement's constant, 1 when absent) multiplies what both sublayers add to the stream; the
+    product joins in one float multiply-add inside the norm kernel that reads the sum next.  With a factor other than 1
+    the products' norm epilogues are not used.  A layer whose feed-forward is "none" has only the first line."""
+
+    def __init__(self, params=None, **parts):
+        super().__init__(params=params, **parts)
+        self.mult = float(self.params.get("residual_mult", 1.0))
+        self.has_ff = not isinstance(self.feed_forward, NoFeedForward)
+
+    def _left(self):
+        return True if self.mult == 1.0 else ScaledAddition(self.mult)
+
     def accepts_prenormed(self, n_tokens):
+        if self.mult != 1.0 or not self.has_ff:
+            return None
         return self.mixer_norm.split() if self.mixer.fuses_norm(n_tokens) else None
 
     def workspace_bytes(self, n_tokens, n_reqs, hidden, dtype):
@@ -38,15 +53,21 @@ class PreNormBlock(Block):
         if isinstance(pending, ops.RowScale):
             x, scale_kw = delta, {"x_scale": pending}
         else:
-            self.mixer_norm.forward(residual, delta if pending else None, h)
+            came = pending_mult(pending)               # norms of other makes know no factor; they are asked only for one
+            self.mixer_norm.forward(residual, delta if pending else None, h, **({} if came == 1.0 else {"mult": came}))
             x, scale_kw = h, {}
+        if not self.has_ff:
+            self.mixer.forward(x, delta, step, cache, writes_cache, ws, **scale_kw)
+            ws.release(mark)
+            return self._left()
         inner = self.feed_forward_norm.split()
-        if inner is None or carry is None or not (self.mixer.fuses_norm(n) and self.feed_forward.fuses_norm(n)):
+        if (self.mult != 1.0 or inner is None or carry is None
+                or not (self.mixer.fuses_norm(n) and self.feed_forward.fuses_norm(n))):
             self.mixer.forward(x, mixed, step, cache, writes_cache, ws, **scale_kw)
-            self.feed_forward_norm.forward(residual, mixed, h)
+            self.feed_forward_norm.forward(residual, mixed, h, **({} if self.mult == 1.0 else {"mult": self.mult}))
             self.feed_forward.forward(h, delta, step, ws)
             ws.release(mark)
-            return True
+            return self._left()
         # the mixer's last product ends its branch: residual += ..., mixed = residual * gain
         sumsq = ws.take((ops.sumsq_parts(hidden), n), torch.float32)
         ends = ops.ResidualNorm(residual, inner[0], sumsq, inner[1])

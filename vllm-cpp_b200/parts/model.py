@@ -19,12 +19,12 @@ import torch
 
 from ..config.model_spec import ModelSpec
 from ..csrc import ops
-from .base import BLOCKS, FAMILIES, NORMS, ParamSpec, StepContext, Workspace, build_part
+from .base import BLOCKS, FAMILIES, NORMS, ParamSpec, StepContext, Workspace, ScaledAddition, build_part, pending_mult
 # importing the modules registers the built-in parts
 from . import (attention as _attention, biased_attention as _biased, block as _block, gate as _gate,  # noqa: F401
                latent_attention as _latent, linear_attention as _linear, mlp as _mlp, moe as _moe, norm as _norm,
                gated_recurrence as _gated_recurrence, parallel as _parallel, position as _position, scale as _scale,
-               shift as _shift, sink_attention as _sink_attention, streams as _streams)
+               shift as _shift, sink_attention as _sink_attention, streams as _streams, talking_attention as _talking)
 
 TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
@@ -166,7 +166,8 @@ class DecoderModel:
         pending = False                 # what delta holds: see Block.forward
         order = self.spec.run_order
         for i, call in enumerate(order):
-            following = self.blocks[order[i + 1].layer] if i + 1 < len(order) else None
+            pending = self.before_call(i, residual, delta, pending, step, ws)
+            following = self.blocks[order[i + 1].layer] if i + 1 < len(order) and not self.interrupts(i + 1) else None
             extra = {"state": caches[call.state]} if call.state >= 0 else {}
             pending = self.blocks[call.layer].forward(residual, delta, pending, step, caches[call.cache],
                                                       call.writes_cache, ws, next_block=following, carry=carry, **extra)
@@ -175,7 +176,8 @@ class DecoderModel:
         out = logits[:m]
         if m:
             normed = ws.take((m, self.hidden), self.dtype)
-            self.final_rows(residual, delta if has_delta else None, normed, step)
+            mult = pending_mult(pending)
+            self.final_rows(residual, delta if has_delta else None, normed, step, **({} if mult == 1.0 else {"mult": mult}))
             self.head(normed, out)
         return out
 
@@ -185,9 +187,21 @@ class DecoderModel:
         """Shape of the float32 residual stream of a step (what the blocks receive as ``residual``)."""
         return (n_tokens, self.hidden)
 
-    def final_rows(self, residual: torch.Tensor, delta: Optional[torch.Tensor], normed: torch.Tensor, step: StepContext) -> None:
-        """normed = the model's final norm of the rows whose logits are wanted (``delta``: an addition still pending)."""
-        self.final_norm.forward(residual, delta, normed, step.logit_rows)
+    def final_rows(self, residual: torch.Tensor, delta: Optional[torch.Tensor], normed: torch.Tensor, step: StepContext,
+                   mult: float = 1.0) -> None:
+        """normed = the model's final norm of the rows whose logits are wanted (``delta``: an addition still pending, which
+        joins times ``mult``)."""
+        self.final_norm.forward(residual, delta, normed, step.logit_rows, **({} if mult == 1.0 else {"mult": mult}))
+
+    def interrupts(self, i: int) -> bool:
+        """True if the model does something of its own to the residual stream right before entry ``i`` of the run order
+        (``before_call``): the block before it then may not prepare that entry's input."""
+        return False
+
+    def before_call(self, i: int, residual: torch.Tensor, delta: torch.Tensor, pending, step: StepContext, ws: Workspace):
+        """Called before entry ``i`` of the run order with what the entry before left (see Block.forward for ``pending``);
+        returns the ``pending`` the entry's block receives.  The plain decoder does nothing here."""
+        return pending
 
     def embed_tokens(self, step: StepContext, residual: torch.Tensor) -> None:
         """residual[t] = the embedding of token t in float32 (src/kernels/embedding_kernel.cu:20-28: no scaling)."""
@@ -206,8 +220,14 @@ class DecoderModel:
         for d in self.residual_shape(n_tokens)[:-1]:
             rows *= d
         own = r(rows * self.hidden * 4) + r(n_tokens * self.hidden * el) \
-            + r(2 * ops.sumsq_parts(self.hidden) * n_tokens * 4) + r(n_logit_rows * self.hidden * el)
+            + r(2 * ops.sumsq_parts(self.hidden) * n_tokens * 4) + r(n_logit_rows * self.hidden * el) \
+            + self.own_workspace_bytes(n_tokens)
         return own + max((blk.workspace_bytes(n_tokens, n_reqs, self.hidden, self.dtype) for blk in self.blocks), default=0)
+
+
+    def own_workspace_bytes(self, n_tokens: int) -> int:
+        """What a model class takes from the workspace beside the plain decoder's buffers."""
+        return 0
 
 
 MODEL_CLASSES["decoder"] = DecoderModel
@@ -283,3 +303,68 @@ class StreamDecoderModel(DecoderModel):
         if delta is not None:
             raise ValueError("stream_decoder: its layers leave no addition pending")
         self.final_norm.forward_streams(residual, self._ones, normed, step.logit_rows)
+
+
+@register_model_class("reentrant_decoder")
+class ReentrantDecoderModel(DecoderModel):
+    """A decoder that re-makes its residual stream from the stream itself and the embedding output x0 at given places of
+    the run order:  x <- W [x ; x0]  with one matrix W [width, 2 * width] (x's columns first), right before each entry
+    that ``ModelSpec.model_params["reentries"]`` lists (the first layer of every pass of a looped run of layers).  The
+    tensor's name is ``model_params["reentry_tensor"]``.  An addition still pending is made first, in float; x and x0
+    enter the product in the compute type and the result is the new float32 stream.  x0 is kept for the step."""
+
+    def __init__(self, spec, dtype, device):
+        super().__init__(spec, dtype, device)
+        p = spec.model_params
+        self.reentries = frozenset(int(i) for i in p.get("reentries", ()))
+        self.reentry_tensor = str(p.get("reentry_tensor", "reentry"))
+        bad = [i for i in self.reentries if not 0 <= i < len(spec.run_order)]
+        if bad:
+            raise ValueError(f"reentrant_decoder: reentries {bad} are no entries of the run order")
+        self.w_reentry: Optional[torch.Tensor] = None
+        self._pair = None                      # [x | x0] of the step in the compute type, the product's input
+        self._have_x0 = False
+
+    def param_specs(self):
+        out = super().param_specs()
+        if self.reentries:
+            out[self.reentry_tensor] = ParamSpec((self.hidden, 2 * self.hidden))
+        return out
+
+    def load_params(self, tensors):
+        super().load_params(tensors)
+        if self.reentries:
+            self.w_reentry = tensors[self.reentry_tensor].contiguous()
+
+    def tensors(self):
+        return super().tensors() + ([self.w_reentry] if self.w_reentry is not None else [])
+
+    def weight_bytes(self):
+        extra = len(self.reentries) * self.w_reentry.numel() * self.w_reentry.element_size() if self.w_reentry is not None else 0
+        return super().weight_bytes() + extra
+
+    def own_workspace_bytes(self, n_tokens):
+        el = torch.empty((), dtype=self.dtype).element_size()
+        return (n_tokens * 2 * self.hidden * el + 255) // 256 * 256 if self.reentries else 0
+
+    def forward(self, step, caches, ws, logits):
+        self._pair = ws.take((step.n_tokens, 2 * self.hidden), self.dtype) if self.reentries else None
+        self._have_x0 = False
+        return super().forward(step, caches, ws, logits)
+
+    def interrupts(self, i):
+        return i in self.reentries
+
+    def before_call(self, i, residual, delta, pending, step, ws):
+        if self.reentries and not self._have_x0:
+            # called first before entry 0, when the stream still is the embedding output: its rows in the compute type
+            # are the right half of the product's input for the whole step
+            ops.cast_rows(residual, None, 1.0, self._pair[:, self.hidden:])
+            self._have_x0 = True
+        if i not in self.reentries:
+            return pending
+        if pending is not False and pending is not True and not isinstance(pending, ScaledAddition):
+            raise ValueError("reentrant_decoder: the block before a reentry must leave the stream or an addition to it")
+        ops.cast_rows(residual, delta if pending else None, pending_mult(pending), self._pair[:, :self.hidden])
+        ops.linear(self._pair, self.w_reentry, residual)
+        return False

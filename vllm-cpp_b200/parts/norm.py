@@ -39,8 +39,8 @@ class RMSNorm(Norm):
     def split(self):
         return (self.weight, self.eps) if self.weight is not None and self.weight.dtype == torch.float32 else None
 
-    def forward(self, residual, delta, out, row_index=None):
-        ops.add_rmsnorm(residual, delta, self.weight, out, self.eps, row_index)
+    def forward(self, residual, delta, out, row_index=None, mult=1.0):
+        ops.add_rmsnorm(residual, delta, self.weight, out, self.eps, row_index, mult)
 
     def add_normed(self, y, gate, gate_bias, residual, plain, mult):
         ops.gated_norm_residual(y, gate, gate_bias, self.weight, residual, plain, mult, self.eps)
@@ -67,8 +67,8 @@ class ScalarRMSNorm(Norm):
         self.gain = tensors[""].reshape(1).to(torch.float32).contiguous()
         self.weight = (self.gain * self.out_scale).expand(self.size).contiguous()
 
-    def forward(self, residual, delta, out, row_index=None):
-        ops.add_rmsnorm(residual, delta, self.weight, out, self.eps, row_index)
+    def forward(self, residual, delta, out, row_index=None, mult=1.0):
+        ops.add_rmsnorm(residual, delta, self.weight, out, self.eps, row_index, mult)
 
     def add_normed(self, y, gate, gate_bias, residual, plain, mult):
         ops.gated_norm_residual(y, gate, gate_bias, self.gain, residual, plain, mult * self.out_scale, self.eps)
@@ -103,7 +103,9 @@ class LayerNorm(Norm):
         """out = norm(sum_s coef[s] streams[s]); streams float32 [S, n, size]."""
         ops.stream_norm(streams, coef, self.weight, self.bias, out, self.eps, row_index, self.out_scale)
 
-    def forward(self, residual, delta, out, row_index=None):
+    def forward(self, residual, delta, out, row_index=None, mult=1.0):
+        if mult != 1.0:
+            raise ValueError("layernorm: a pending addition joins with factor 1 only")
         x = residual.unsqueeze(0)
         if delta is not None:
             if row_index is not None:

@@ -1,0 +1,101 @@
+"""Grouped-query attention over the paged cache whose heads talk to one another before the softmax, without
+rotation and without a value projection:
+
+    q = W_q h,  k = W_k h                            heads of ``head_dim``; query head g reads kv head g // (heads / kv_heads)
+    v = k                                            the values are the keys as projected
+    qn, kn = q, k divided by their root mean square per head (eps inside the root; no gain)
+    raw_g(i, j) = scale * (qn_i,g . kn_j) - slope_g * (i - j),   slope_g = 2^(-slope_span * (g + 1) / heads)
+    s_h(i, j)   = sum_g talk[h, g] * raw_g(i, j)     the heads' scores mixed by a learned heads x heads matrix
+    out = W_o (concat_h(softmax_j(s_h) v) * sigmoid(W_g h))
+
+``slope_span`` 0 switches the distance bias off, ``talk`` False the mixing (the identity is used), ``qk_norm`` False
+the division, ``output_gate`` False the gate; ``window`` > 0 restricts a query to the last ``window`` keys.  The cache
+holds the normed keys in its key plane and the keys as projected in its value plane.  q, k and the gate are one product;
+the norms and the cache write are the kernel that attention with head norms uses (csrc/attention_biased.cu,
+qk_head_rope_cache_write_kernel with a gain of ones and no rotation); attention is csrc/attention_talking.cu.  Scores,
+bias, mixing, softmax and the weighted sums are float in both precisions.  The reference's attention
+(src/layers/attention.cpp) has independent heads, rotation and a value projection.
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import numpy as np
+import torch
+
+from ..csrc import ops
+from .base import Mixer, PagedKVSpec, ParamSpec, register_mixer, workspace_piece
+
+
+def distance_slopes(heads: int, span: float) -> np.ndarray:
+    """slope_g = 2^(-span * (g + 1) / heads) for g = 0 .. heads - 1, in double."""
+    return np.power(2.0, -float(span) * (np.arange(heads, dtype=np.float64) + 1.0) / heads)
+
+
+@register_mixer("talking_heads_attention")
+class TalkingHeadsAttention(Mixer):
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float, eps: float, dtype, device,
+                 slope_span: float = 8.0, talk: bool = True, qk_norm: bool = True, output_gate: bool = True, window: int = 0):
+        if min(hidden_size, num_heads, num_kv_heads, head_dim) <= 0 or num_heads % num_kv_heads:
+            raise ValueError(f"talking_heads_attention: {num_heads} heads cannot share {num_kv_heads} kv heads")
+        if num_heads > ops.TALKING_MAX_HEADS or head_dim > 256:
+            raise ValueError(f"talking_heads_attention: at most {ops.TALKING_MAX_HEADS} heads of at most 256")
+        if window < 0 or slope_span < 0 or not eps > 0:
+            raise ValueError("talking_heads_attention: window and slope_span must not be negative, eps positive")
+        self.hidden, self.nh, self.nkv, self.d = hidden_size, num_heads, num_kv_heads, head_dim
+        self.scale, self.eps, self.window, self.slope_span = float(scale), float(eps), int(window), float(slope_span)
+        self.talk, self.qk_norm, self.output_gate = bool(talk), bool(qk_norm), bool(output_gate)
+        self.dtype, self.device = dtype, device
+        self.w_in = self.w_o = self.mix = self.slopes = self.ones = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        specs = {"q": ParamSpec((self.nh * self.d, self.hidden)), "k": ParamSpec((self.nkv * self.d, self.hidden))}
+        if self.talk:
+            specs["talk"] = ParamSpec((self.nh, self.nh), "identity")
+        if self.output_gate:
+            specs["g"] = ParamSpec((self.nh * self.d, self.hidden))
+        specs["o"] = ParamSpec((self.hidden, self.nh * self.d))
+        return specs
+
+    def load_params(self, tensors):
+        rows = [tensors["q"], tensors["k"]] + ([tensors["g"]] if self.output_gate else [])
+        self.w_in = torch.cat(rows, dim=0).contiguous()
+        self.w_o = tensors["o"].contiguous()
+        dev = self.w_o.device
+        self.mix = (tensors["talk"].to(torch.float32) if self.talk else torch.eye(self.nh, dtype=torch.float32, device=dev)).contiguous()
+        self.slopes = (torch.from_numpy(distance_slopes(self.nh, self.slope_span).astype(np.float32)).to(dev)
+                       if self.slope_span > 0 else None)
+        self.ones = torch.ones(self.d, dtype=torch.float32, device=dev) if self.qk_norm else None
+
+    def product_weights(self):
+        return [(self.w_in, 0), (self.w_o, 0)]
+
+    def cache_spec(self):
+        return PagedKVSpec(self.nkv, self.d, self.window)
+
+    def in_width(self) -> int:
+        return (self.nh + self.nkv) * self.d + (self.nh * self.d if self.output_gate else 0)
+
+    def workspace_bytes(self, n_tokens, n_reqs):
+        return workspace_piece((n_tokens, self.in_width()), self.dtype) + 2 * workspace_piece((n_tokens, self.nh * self.d), self.dtype)
+
+    def forward(self, x, out, step, cache, writes_cache, ws):
+        n = x.shape[0]
+        mark = ws.mark()
+        proj = ws.take((n, self.in_width()), self.dtype)
+        ops.linear(x, self.w_in, proj)
+        k_off = self.nh * self.d
+        g_off = k_off + self.nkv * self.d
+        block_table = step.block_tables[cache.group]
+        pages = cache.pages.view(cache.pages.shape[0], -1)
+        sizes = dict(num_heads=self.nh, num_kv_heads=self.nkv, head_dim=self.d, v_head_dim=self.d, row=self.d, page_size=cache.page_size)
+        q = ws.take((n, self.nh * self.d), self.dtype)
+        # keys normed per head into the key plane, the same keys as projected into the value plane
+        ops.qk_head_rope_cache_write(proj, 0, k_off, k_off, self.ones, self.ones, None, q, pages, step.positions, step.req_of_token,
+                                     block_table, eps=self.eps, write_kv=writes_cache, **sizes)
+        attn = ws.take((n, self.nh * self.d), self.dtype)
+        gate = proj[:, g_off:] if self.output_gate else None
+        ops.attention_talking(q, pages, attn, gate, step.positions, step.req_of_token, block_table, self.mix, self.slopes,
+                              window=self.window, scale=self.scale, **sizes)
+        ops.linear(attn, self.w_o, out)
+        ws.release(mark)
