@@ -11,6 +11,13 @@
 //
 //   attention_talking_kernel        the plain form: a CTA per token, a warp per head, a key per lane; the heads' raw
 //                                   scores of 32 keys meet in shared memory, where every warp mixes its own row
+//   attention_talking_mma_kernel    bfloat16 heads of 64 or 128 on tensor cores (mma.sync m16n8k16, float accumulation):
+//                                   a CTA per work item (16 query rows of a request and a run of its keys), a warp per
+//                                   head; per tile of 32 keys every warp takes its head's 16 x 32 raw scores, leaves them
+//                                   in shared memory, mixes its own row of the heads' matrix from there in float, runs the
+//                                   online softmax on its fragments and multiplies the weights, as two bfloat16 terms
+//                                   (16 bits of mantissa), with the value tile.  A work item that holds only part of a
+//                                   row's keys leaves (o, m, l) partials; attention_talking_merge_kernel joins them.
 //
 // The reference's attention (src/attention/paged_attention.cu) has independent heads.
 #include "common.cuh"
@@ -150,5 +157,328 @@ VCB_EXPORT int vcb_attention_talking(const void* q, const void* cache, void* out
         if (smem > 48 * 1024) { const int e = vcb_allow_dynamic_smem(attention_talking_kernel<__nv_bfloat16>, (int)smem, &done_b); if (e) return e; }
         vcb_launch(attention_talking_kernel<__nv_bfloat16>, n_tokens, H * 32, smem, s, a);
     } else return VCB_ERR_BAD_ARG;
+    return vcb_last_error();
+}
+
+// ------------------------------------------------------------------ tensor cores (bfloat16, heads of 64 or 128)
+#define TKM_ROWS 16            // query rows of a work item
+#define TKM_KEYS 32            // keys of a tile
+#define TKM_RAW_LD 40          // floats between two rows of the raw scores in shared memory (conflict-free 64-bit accesses)
+#define TKM_MAX_HEADS 16       // a warp per head, and a head's fragments want more registers than 1024 threads leave
+#define TKM_ITEM_INTS 6        // request, first row within the request's rows of this step, rows, first key, end of keys, partial slot or -1
+
+struct TalkingMmaArgs {
+    const __nv_bfloat16* q;     // [n, H * D]
+    const __nv_bfloat16* cache;
+    __nv_bfloat16* out;         // [n, H * D]
+    const __nv_bfloat16* gate;  // [n, H * D] rows ldg apart, or null
+    long long ldg;
+    const int* items;           // [n_items, TKM_ITEM_INTS]
+    const int* q_start;         // [n_reqs + 1] first row of each request in this step
+    const int* ctx_lens;        // [n_reqs] keys in the cache before this step
+    const int* block_table;
+    const float* mix;           // [H, H]
+    const float* slope;         // [H] or null
+    float* part_o;              // [slots, H, TKM_ROWS... see below] partial sums of a split item: [slot][h][D]
+    float* part_ml;             // [slot][h][2]
+    int bt_stride, H, G, page, window, num_pages;
+    float scale;
+    int* status;
+};
+
+__device__ __forceinline__ void tkm_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t tkm_pack(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// The part of x that its bfloat16 rounding leaves out, so that hi + lo carries 16 bits of x's mantissa.
+__device__ __forceinline__ float tkm_rest(float x) { return x - __bfloat162float(__float2bfloat16_rn(x)); }
+
+template <int D, int MAXT>
+__global__ void __launch_bounds__(MAXT) attention_talking_mma_kernel(TalkingMmaArgs a) {
+    constexpr int LDK = D + 8;                      // bfloat16 elements between two keys of a tile in shared memory
+    extern __shared__ __align__(16) unsigned char tkm_smem[];
+    __nv_bfloat16* ks = reinterpret_cast<__nv_bfloat16*>(tkm_smem);                 // [G][TKM_KEYS][LDK] normed keys
+    __nv_bfloat16* vs = ks + (size_t)a.G * TKM_KEYS * LDK;                          // [G][TKM_KEYS][LDK] values
+    float* raw = reinterpret_cast<float*>(vs + (size_t)a.G * TKM_KEYS * LDK);      // [H][TKM_ROWS][TKM_RAW_LD]
+    float* mixs = raw + (size_t)a.H * TKM_ROWS * TKM_RAW_LD;                        // [H][H]
+    pdl_start();
+    const int h = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int gr = lane >> 2, tq = lane & 3;        // fragment row (and row + 8) and column pair of this lane
+    const int* item = a.items + (size_t)blockIdx.x * TKM_ITEM_INTS;
+    const int req = item[0], q0 = item[1], nq = item[2], k_lo = item[3], k_hi = item[4], slot_out = item[5];
+    const int g = h / (a.H / a.G);
+    const int row0 = a.q_start[req] + q0;           // first row of the item among the step's tokens
+    const int pos0 = a.ctx_lens[req] + q0;          // its position in the request
+    const int* bt = a.block_table + (size_t)req * a.bt_stride;
+    for (int i = threadIdx.x; i < a.H * a.H; i += blockDim.x) mixs[i] = a.mix[i];
+    const float slope = a.slope ? a.slope[h] : 0.0f;
+
+    // the head's queries as A fragments: rows gr and gr + 8, D / 16 steps of 16 coordinates
+    uint32_t qf[D / 16][4];
+    {
+        const __nv_bfloat16* qa = a.q + ((size_t)(row0 + gr) * a.H + h) * D + tq * 2;
+        const __nv_bfloat16* qb = qa + (size_t)8 * a.H * D;
+        const bool ra = gr < nq, rb = gr + 8 < nq;
+#pragma unroll
+        for (int s = 0; s < D / 16; ++s) {
+            qf[s][0] = ra ? *reinterpret_cast<const uint32_t*>(qa + s * 16) : 0u;
+            qf[s][1] = rb ? *reinterpret_cast<const uint32_t*>(qb + s * 16) : 0u;
+            qf[s][2] = ra ? *reinterpret_cast<const uint32_t*>(qa + s * 16 + 8) : 0u;
+            qf[s][3] = rb ? *reinterpret_cast<const uint32_t*>(qb + s * 16 + 8) : 0u;
+        }
+    }
+    float o[D / 8][4];
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.0f, l_b = 0.0f;     // rows gr and gr + 8
+    const int pos_a = pos0 + gr, pos_b = pos0 + gr + 8;
+    const bool row_a = gr < nq, row_b = gr + 8 < nq;
+
+    const size_t block = (size_t)a.page * D;
+    const size_t page_elems = 2 * (size_t)a.G * block;
+    constexpr int CH = D / 8;                       // 16-byte chunks of a key
+    const int n_chunks = a.G * TKM_KEYS * CH;
+
+    for (int k0 = k_lo; k0 < k_hi; k0 += TKM_KEYS) {
+        __syncthreads();                            // the tile before is read no more (and mixs is in place)
+        // the tile's keys and values of every kv head, out of their pages into rows of LDK elements
+        for (int c = threadIdx.x; c < n_chunks; c += blockDim.x) {
+            const int gk = c / (TKM_KEYS * CH), rem = c - gk * (TKM_KEYS * CH);
+            const int key = rem / CH, ch = rem - key * CH;
+            const int j = k0 + key;
+            uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
+            if (j < k_hi) {
+                const int lp = j / a.page, sl = j - lp * a.page;
+                const int pg = lp < a.bt_stride ? bt[lp] : -1;
+                if ((unsigned)pg >= (unsigned)a.num_pages) {
+                    if (a.status) atomicCAS(a.status, 0, VCB_STATUS_BAD_PAGE);
+                } else {
+                    const __nv_bfloat16* src = a.cache + (size_t)pg * page_elems + (size_t)gk * block + kv_pos(ch * 8, sl, D, a.page, 2);
+                    kv = *reinterpret_cast<const uint4*>(src);
+                    vv = *reinterpret_cast<const uint4*>(src + (size_t)a.G * block);
+                }
+            }
+            *reinterpret_cast<uint4*>(ks + ((size_t)gk * TKM_KEYS + key) * LDK + ch * 8) = kv;
+            *reinterpret_cast<uint4*>(vs + ((size_t)gk * TKM_KEYS + key) * LDK + ch * 8) = vv;
+        }
+        __syncthreads();
+        // raw scores of this warp's head: 16 rows x 32 keys
+        float sc[TKM_KEYS / 8][4];
+#pragma unroll
+        for (int n = 0; n < TKM_KEYS / 8; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.0f;
+        const __nv_bfloat16* kh = ks + (size_t)g * TKM_KEYS * LDK;
+#pragma unroll
+        for (int s = 0; s < D / 16; ++s) {
+#pragma unroll
+            for (int n = 0; n < TKM_KEYS / 8; ++n) {
+                const __nv_bfloat16* kp = kh + (size_t)(n * 8 + gr) * LDK + s * 16 + tq * 2;
+                tkm_mma(sc[n], qf[s], *reinterpret_cast<const uint32_t*>(kp), *reinterpret_cast<const uint32_t*>(kp + 8));
+            }
+        }
+        // scale, distance bias, and into shared memory for the other heads (a key no row sees, or beyond the item: 0)
+        float* mine = raw + (size_t)h * TKM_ROWS * TKM_RAW_LD;
+#pragma unroll
+        for (int n = 0; n < TKM_KEYS / 8; ++n) {
+            const int j = k0 + n * 8 + tq * 2;
+            float2 ra, rb;
+            ra.x = sc[n][0] * a.scale - slope * (float)(pos_a - j);
+            ra.y = sc[n][1] * a.scale - slope * (float)(pos_a - j - 1);
+            rb.x = sc[n][2] * a.scale - slope * (float)(pos_b - j);
+            rb.y = sc[n][3] * a.scale - slope * (float)(pos_b - j - 1);
+            *reinterpret_cast<float2*>(mine + gr * TKM_RAW_LD + n * 8 + tq * 2) = ra;
+            *reinterpret_cast<float2*>(mine + (gr + 8) * TKM_RAW_LD + n * 8 + tq * 2) = rb;
+        }
+        __syncthreads();
+        // this head's mixed scores, in the fragments' places
+#pragma unroll
+        for (int n = 0; n < TKM_KEYS / 8; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.0f;
+        for (int gg = 0; gg < a.H; ++gg) {
+            const float w = mixs[h * a.H + gg];
+            const float* theirs = raw + (size_t)gg * TKM_ROWS * TKM_RAW_LD;
+#pragma unroll
+            for (int n = 0; n < TKM_KEYS / 8; ++n) {
+                const float2 ra = *reinterpret_cast<const float2*>(theirs + gr * TKM_RAW_LD + n * 8 + tq * 2);
+                const float2 rb = *reinterpret_cast<const float2*>(theirs + (gr + 8) * TKM_RAW_LD + n * 8 + tq * 2);
+                sc[n][0] = fmaf(w, ra.x, sc[n][0]);
+                sc[n][1] = fmaf(w, ra.y, sc[n][1]);
+                sc[n][2] = fmaf(w, rb.x, sc[n][2]);
+                sc[n][3] = fmaf(w, rb.y, sc[n][3]);
+            }
+        }
+        // what a row may see: keys up to its own position (and inside its window), below the item's end
+        float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < TKM_KEYS / 8; ++n) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int j = k0 + n * 8 + tq * 2 + e;
+                const bool in = j < k_hi;
+                const bool see_a = in && row_a && j <= pos_a && (a.window <= 0 || pos_a - j < a.window);
+                const bool see_b = in && row_b && j <= pos_b && (a.window <= 0 || pos_b - j < a.window);
+                if (!see_a) sc[n][e] = -INFINITY;
+                if (!see_b) sc[n][2 + e] = -INFINITY;
+                mx_a = fmaxf(mx_a, sc[n][e]);
+                mx_b = fmaxf(mx_b, sc[n][2 + e]);
+            }
+        }
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+        const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+        const float ca = mn_a == -INFINITY ? 1.0f : expf(m_a - mn_a), cb = mn_b == -INFINITY ? 1.0f : expf(m_b - mn_b);
+        float sum_a = 0.0f, sum_b = 0.0f;
+#pragma unroll
+        for (int n = 0; n < TKM_KEYS / 8; ++n) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const float pa = sc[n][e] == -INFINITY ? 0.0f : expf(sc[n][e] - mn_a);
+                const float pb = sc[n][2 + e] == -INFINITY ? 0.0f : expf(sc[n][2 + e] - mn_b);
+                sc[n][e] = pa;
+                sc[n][2 + e] = pb;
+                sum_a += pa;
+                sum_b += pb;
+            }
+        }
+        sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 1);
+        sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 2);
+        sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 1);
+        sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 2);
+        l_a = l_a * ca + sum_a;
+        l_b = l_b * cb + sum_b;
+        m_a = mn_a;
+        m_b = mn_b;
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n) { o[n][0] *= ca; o[n][1] *= ca; o[n][2] *= cb; o[n][3] *= cb; }
+        // weights x values: the weights as A fragments in two bfloat16 terms, the values' tile read transposed
+        const __nv_bfloat16* vh = vs + (size_t)g * TKM_KEYS * LDK;
+#pragma unroll
+        for (int s = 0; s < TKM_KEYS / 16; ++s) {
+            uint32_t hi[4], lo[4];
+            hi[0] = tkm_pack(sc[2 * s][0], sc[2 * s][1]);
+            hi[1] = tkm_pack(sc[2 * s][2], sc[2 * s][3]);
+            hi[2] = tkm_pack(sc[2 * s + 1][0], sc[2 * s + 1][1]);
+            hi[3] = tkm_pack(sc[2 * s + 1][2], sc[2 * s + 1][3]);
+            lo[0] = tkm_pack(tkm_rest(sc[2 * s][0]), tkm_rest(sc[2 * s][1]));
+            lo[1] = tkm_pack(tkm_rest(sc[2 * s][2]), tkm_rest(sc[2 * s][3]));
+            lo[2] = tkm_pack(tkm_rest(sc[2 * s + 1][0]), tkm_rest(sc[2 * s + 1][1]));
+            lo[3] = tkm_pack(tkm_rest(sc[2 * s + 1][2]), tkm_rest(sc[2 * s + 1][3]));
+            const uint32_t vrow = cx_smem(vh + (size_t)(s * 16 + (lane & 15)) * LDK);
+#pragma unroll
+            for (int n = 0; n < D / 8; ++n) {
+                uint32_t b0, b1;
+                asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(b0), "=r"(b1) : "r"(vrow + n * 16));
+                tkm_mma(o[n], hi, b0, b1);
+                tkm_mma(o[n], lo, b0, b1);
+            }
+        }
+    }
+    if (slot_out >= 0) {
+        // part of a row's keys (single rows only): the sums as they stand, with their reference and weight
+        if (gr == 0) {
+            float* po = a.part_o + ((size_t)slot_out * a.H + h) * D;
+#pragma unroll
+            for (int n = 0; n < D / 8; ++n) *reinterpret_cast<float2*>(po + n * 8 + tq * 2) = make_float2(o[n][0], o[n][1]);
+            if (tq == 0) {
+                a.part_ml[((size_t)slot_out * a.H + h) * 2] = m_a;
+                a.part_ml[((size_t)slot_out * a.H + h) * 2 + 1] = l_a;
+            }
+        }
+        return;
+    }
+    const float inv_a = l_a > 0.0f ? 1.0f / l_a : 0.0f, inv_b = l_b > 0.0f ? 1.0f / l_b : 0.0f;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = gr + 8 * half;
+        if (r >= nq) continue;
+        const float inv = half ? inv_b : inv_a;
+        __nv_bfloat16* orow = a.out + ((size_t)(row0 + r) * a.H + h) * D;
+        const __nv_bfloat16* grow = a.gate ? a.gate + (size_t)(row0 + r) * a.ldg + (size_t)h * D : nullptr;
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n) {
+            float y0 = o[n][2 * half] * inv, y1 = o[n][2 * half + 1] * inv;
+            if (grow) {
+                const float2 gt = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(grow + n * 8 + tq * 2));
+                y0 *= 1.0f / (1.0f + expf(-gt.x));
+                y1 *= 1.0f / (1.0f + expf(-gt.y));
+            }
+            *reinterpret_cast<__nv_bfloat162*>(orow + n * 8 + tq * 2) = __floats2bfloat162_rn(y0, y1);
+        }
+    }
+}
+
+// Joins the partial sums of single-row items: request r's row was cut into `nsplit` runs of keys, whose partials lie
+// in slots r * nsplit .. r * nsplit + nsplit - 1.  A CTA per request, a warp per head.
+__global__ void attention_talking_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                               __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gate, long long ldg,
+                                               const int* __restrict__ q_start, int H, int D, int nsplit) {
+    pdl_start();
+    const int r = blockIdx.x, h = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (h >= H) return;
+    float m = -INFINITY;
+    for (int s = 0; s < nsplit; ++s) m = fmaxf(m, part_ml[(((size_t)r * nsplit + s) * H + h) * 2]);
+    float l = 0.0f;
+    for (int s = 0; s < nsplit; ++s) {
+        const float* ml = part_ml + (((size_t)r * nsplit + s) * H + h) * 2;
+        if (ml[0] != -INFINITY) l += ml[1] * expf(ml[0] - m);
+    }
+    const int row = q_start[r];
+    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+    for (int i = lane; i < D; i += 32) {
+        float acc = 0.0f;
+        for (int s = 0; s < nsplit; ++s) {
+            const size_t at = ((size_t)r * nsplit + s) * H + h;
+            const float ms = part_ml[at * 2];
+            if (ms != -INFINITY) acc = fmaf(part_o[at * D + i], expf(ms - m), acc);
+        }
+        float y = acc * inv;
+        if (gate) y *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)row * ldg + (size_t)h * D + i])));
+        out[((size_t)row * H + h) * D + i] = __float2bfloat16_rn(y);
+    }
+}
+
+VCB_EXPORT long long vcb_attention_talking_mma_smem(int H, int G, int D) {
+    return (long long)2 * G * TKM_KEYS * (D + 8) * 2 + (long long)H * TKM_ROWS * TKM_RAW_LD * 4 + (long long)H * H * 4;
+}
+
+// items: [n_items, 6] as TalkingMmaArgs says.  nsplit > 1: every item is one row of a request cut into nsplit runs
+// (slot = request * nsplit + run), and the merge kernel writes the n_reqs rows.
+VCB_EXPORT int vcb_attention_talking_mma(const void* q, const void* cache, void* out, const void* gate, long long ldg,
+                                         const int* items, int n_items, const int* q_start, const int* ctx_lens,
+                                         const int* block_table, int bt_stride, const float* mix, const float* slope,
+                                         float* part_o, float* part_ml, int nsplit, int n_reqs, int H, int G, int D, int page,
+                                         int window, float scale, int num_pages, int* status, void* stream) {
+    if (n_items <= 0) return 0;
+    if (!q || !cache || !out || !items || !mix || H <= 0 || G <= 0 || H % G || page <= 0 || window < 0 || num_pages < 0 || nsplit < 1)
+        return VCB_ERR_BAD_ARG;
+    if (H > TKM_MAX_HEADS || (D != 64 && D != 128)) return VCB_ERR_UNSUPPORTED;
+    if (nsplit > 1 && (!part_o || !part_ml || n_items != n_reqs * nsplit)) return VCB_ERR_BAD_ARG;
+    const long long smem = vcb_attention_talking_mma_smem(H, G, D);
+    if (smem > 220 * 1024) return VCB_ERR_UNSUPPORTED;
+    TalkingMmaArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, (const __nv_bfloat16*)gate, ldg, items,
+                     q_start, ctx_lens, block_table, mix, slope, part_o, part_ml, bt_stride, H, G, page, window, num_pages, scale, status};
+    cudaStream_t s = (cudaStream_t)stream;
+    static unsigned long long done[4] = {0, 0, 0, 0};
+#define TKM_GO(DD, TT, I)                                                                                   \
+    do {                                                                                                    \
+        const int e = vcb_allow_dynamic_smem(attention_talking_mma_kernel<DD, TT>, 220 * 1024, &done[I]);   \
+        if (e) return e;                                                                                    \
+        vcb_launch(attention_talking_mma_kernel<DD, TT>, n_items, H * 32, (size_t)smem, s, a);              \
+    } while (0)
+    if (D == 64 && H <= 8) TKM_GO(64, 256, 0);
+    else if (D == 64) TKM_GO(64, 512, 1);
+    else if (H <= 8) TKM_GO(128, 256, 2);
+    else TKM_GO(128, 512, 3);
+#undef TKM_GO
+    if (nsplit > 1)
+        vcb_launch(attention_talking_merge_kernel, n_reqs, H * 32, 0, s, (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out,
+                   (const __nv_bfloat16*)gate, ldg, q_start, H, D, nsplit);
     return vcb_last_error();
 }

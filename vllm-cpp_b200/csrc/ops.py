@@ -61,6 +61,7 @@ _SIGNATURES = {
     "vcb_clamped_swish_mul": [_P, _P, _P, _I, _I, _F, _F, _F, _I, _P],
     "vcb_moe_router_biased": [_P, _L, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P],
     "vcb_moe_combine_add": [_P, _P, _L, _P, _P, _P, _I, _I, _I, _P, _L, _I, _P],
+    "vcb_attention_talking_mma": [_P, _P, _P, _P, _L, _P, _I, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
     "vcb_attention_talking": [_P, _P, _P, _P, _L, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _I, _P],
     "vcb_attention_decode_mma_shaped": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _I, _F, _P, _I,
                                         _P, _P, _L, _I, _P],
@@ -1471,6 +1472,45 @@ def latent_rope_cache_write(raw: torch.Tensor, gain: torch.Tensor, q: Optional[t
 
 
 TALKING_MAX_HEADS = 32
+TALKING_MMA_MAX_HEADS = 16         # the tensor-core kernel runs a warp per head
+TALKING_MMA_HEAD_DIMS = (64, 128)
+TALKING_ITEM_ROWS = 16             # query rows of a work item of the tensor-core kernel
+TALKING_KEY_TILE = 32
+TALKING_MAX_SPLITS = 32
+TALKING_ITEM_INTS = 6
+
+
+def attention_talking_mma(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor], items: torch.Tensor,
+                          n_items: int, q_start, ctx_lens, block_table, mix: torch.Tensor, slope: Optional[torch.Tensor], *,
+                          nsplit: int, n_reqs: int, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int,
+                          scale: float, part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None) -> None:
+    """attention_talking on tensor cores for bfloat16 heads of 64 or 128 (keys and values of one width).  ``items`` int32
+    [n_items, 6]: (request, first row within the request's rows of this step, rows (at most 16), first key, end of keys,
+    partial slot or -1).  ``nsplit`` > 1: every request brings one row, cut into ``nsplit`` runs of keys whose partial sums
+    (slot = request * nsplit + run) a second kernel joins through ``part_o`` / ``part_ml`` (float32 scratch)."""
+    n = q.shape[0]
+    _need(q.dtype == torch.bfloat16 and cache.dtype == q.dtype and out.dtype == q.dtype, "attention_talking_mma: bfloat16 only")
+    _need(head_dim in TALKING_MMA_HEAD_DIMS and num_heads <= TALKING_MMA_MAX_HEADS, "attention_talking_mma: up to 16 heads of 64 or 128")
+    _need(q.shape == (n, num_heads * head_dim) and out.shape == q.shape, "attention_talking_mma: shapes")
+    _need(mix.shape == (num_heads, num_heads) and mix.is_contiguous(), "attention_talking_mma: mix [heads, heads]")
+    _need(items.dtype == torch.int32 and items.is_contiguous() and items.numel() >= n_items * TALKING_ITEM_INTS, "attention_talking_mma: items")
+    if gate is not None:
+        _rows(gate, "gate", q.dtype)
+        _need(gate.shape == out.shape, "attention_talking_mma: gate like out")
+    if nsplit > 1:
+        need = n_reqs * nsplit * num_heads
+        _need(part_o is not None and part_ml is not None and part_o.numel() >= need * head_dim and part_ml.numel() >= need * 2,
+              "attention_talking_mma: scratch for the partial sums")
+    _check(lib().vcb_attention_talking_mma(
+        _dev(q, "q"), _dev(cache, "cache"), _dev(out, "out"), None if gate is None else gate.data_ptr(),
+        0 if gate is None else gate.stride(0), items.data_ptr(), n_items, _dev(q_start, "q_start", torch.int32),
+        _dev(ctx_lens, "ctx_lens", torch.int32), _dev(block_table, "block_table", torch.int32), block_table.shape[1],
+        _dev(mix, "mix", torch.float32), None if slope is None else _dev(slope, "slope", torch.float32),
+        None if part_o is None else part_o.data_ptr(), None if part_ml is None else part_ml.data_ptr(), nsplit, n_reqs, num_heads,
+        num_kv_heads, head_dim, page_size, window, float(scale), cache.shape[0], status_tensor(q.device).data_ptr(), _stream()),
+        "attention_talking_mma")
+    if nsplit > 1:
+        add_launches(1)
 
 
 def attention_talking(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor], positions,

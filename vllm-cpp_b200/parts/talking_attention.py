@@ -12,8 +12,11 @@ rotation and without a value projection:
 the division, ``output_gate`` False the gate; ``window`` > 0 restricts a query to the last ``window`` keys.  The cache
 holds the normed keys in its key plane and the keys as projected in its value plane.  q, k and the gate are one product;
 the norms and the cache write are the kernel that attention with head norms uses (csrc/attention_biased.cu,
-qk_head_rope_cache_write_kernel with a gain of ones and no rotation); attention is csrc/attention_talking.cu.  Scores,
-bias, mixing, softmax and the weighted sums are float in both precisions.  The reference's attention
+qk_head_rope_cache_write_kernel with a gain of ones and no rotation); attention is csrc/attention_talking.cu: in
+bfloat16 with up to 16 heads of 64 or 128 the tensor-core kernel over work items that the host lists per step (16 query
+rows of a request each; in steps of single tokens a request's keys are cut into runs that fill the device, joined by a
+second kernel), otherwise the plain kernel.  Scores, bias, mixing, softmax and the weighted sums are float in both
+precisions; the tensor cores take the weights as two bfloat16 terms.  The reference's attention
 (src/layers/attention.cpp) has independent heads, rotation and a value projection.
 """
 from __future__ import annotations
@@ -70,6 +73,58 @@ class TalkingHeadsAttention(Mixer):
     def product_weights(self):
         return [(self.w_in, 0), (self.w_o, 0)]
 
+    # -- the tensor-core kernel's work lists
+    def _tensor_core_path(self) -> bool:
+        return (self.dtype == torch.bfloat16 and self.d in ops.TALKING_MMA_HEAD_DIMS and self.nh <= ops.TALKING_MMA_MAX_HEADS)
+
+    def _items_key(self) -> str:
+        return f"talk_items_w{self.window}"
+
+    SPLIT_LADDER = (1, 2, 3, 4, 6, 8, 12, 16, 24, 32)
+
+    def step_arrays(self):
+        """Work items of the tensor-core kernel, [items, 6] int32 (ops.attention_talking_mma): portions in tiles of 16
+        rows, the tiles that see the most keys first; a step of single tokens with every request's keys cut into as
+        many runs (the same number for all, from a short ladder) as fill the device once with two CTAs an SM, a run
+        being at least four key tiles.  The number of items and of runs are launch shapes of the step."""
+        if not self._tensor_core_path():
+            return {}
+        key = self._items_key()
+
+        def items(host):
+            rows, tile = ops.TALKING_ITEM_ROWS, ops.TALKING_KEY_TILE
+            out = []
+            if all(q == 1 for q in host.q_lens):
+                hi = [c + 1 for c in host.ctx_lens]
+                lo = [max(0, h - self.window) if self.window > 0 else 0 for h in hi]
+                longest = max(-(-(h - l) // tile) for h, l in zip(hi, lo))
+                want = max(1, min(2 * ops.sm_count() // len(hi), longest // 4, ops.TALKING_MAX_SPLITS))
+                nsplit = max(s for s in self.SPLIT_LADDER if s <= want)
+                for r, (l, h) in enumerate(zip(lo, hi)):
+                    per = -(-(-(-(h - l) // nsplit)) // tile) * tile           # keys of a run, whole tiles
+                    for s in range(nsplit):
+                        a, b = min(h, l + s * per), min(h, l + (s + 1) * per)
+                        out.append((r, 0, 1, a, b, r * nsplit + s if nsplit > 1 else -1))
+            else:
+                nsplit = 1
+                for r, (q, ctx) in enumerate(zip(host.q_lens, host.ctx_lens)):
+                    for q0 in range(0, q, rows):
+                        nq = min(rows, q - q0)
+                        k_lo = max(0, ctx + q0 - self.window + 1) if self.window > 0 else 0
+                        out.append((r, q0, nq, k_lo, ctx + q0 + nq, -1))
+                out.sort(key=lambda it: it[3] - it[4])                        # the longest first (a stable sort)
+            host.shapes[key] = len(out)
+            host.shapes[key + "_runs"] = nsplit
+            return np.asarray(out, dtype=np.int32).reshape(-1, ops.TALKING_ITEM_INTS)
+
+        return {key: items}
+
+    def reserve(self, n_tokens, n_reqs, device):
+        if self._tensor_core_path():
+            most = n_reqs * ops.TALKING_MAX_SPLITS * self.nh
+            ops.scratch("talk_part_o", most * self.d, device)
+            ops.scratch("talk_part_ml", most * 2, device)
+
     def cache_spec(self):
         return PagedKVSpec(self.nkv, self.d, self.window)
 
@@ -95,7 +150,20 @@ class TalkingHeadsAttention(Mixer):
                                      block_table, eps=self.eps, write_kv=writes_cache, **sizes)
         attn = ws.take((n, self.nh * self.d), self.dtype)
         gate = proj[:, g_off:] if self.output_gate else None
-        ops.attention_talking(q, pages, attn, gate, step.positions, step.req_of_token, block_table, self.mix, self.slopes,
-                              window=self.window, scale=self.scale, **sizes)
+        key = self._items_key()
+        if self._tensor_core_path() and key in step.extras and key in step.shapes:
+            nsplit = step.shapes[key + "_runs"]
+            part_o = part_ml = None
+            if nsplit > 1:
+                need = step.n_reqs * nsplit * self.nh
+                part_o = ops.scratch("talk_part_o", need * self.d, q.device)
+                part_ml = ops.scratch("talk_part_ml", need * 2, q.device)
+            ops.attention_talking_mma(q, pages, attn, gate, step.extras[key], step.shapes[key], step.q_start, step.ctx_lens, block_table,
+                                      self.mix, self.slopes, nsplit=nsplit, n_reqs=step.n_reqs, num_heads=self.nh,
+                                      num_kv_heads=self.nkv, head_dim=self.d, page_size=cache.page_size, window=self.window,
+                                      scale=self.scale, part_o=part_o, part_ml=part_ml)
+        else:
+            ops.attention_talking(q, pages, attn, gate, step.positions, step.req_of_token, block_table, self.mix, self.slopes,
+                                  window=self.window, scale=self.scale, **sizes)
         ops.linear(attn, self.w_o, out)
         ws.release(mark)
