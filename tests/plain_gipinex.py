@@ -131,9 +131,10 @@ def tensor_shapes(cfg):
     return out
 
 
-def random_weights(cfg, seed, std=0.08, gain_std=0.1, sharp=1.0):
+def random_weights(cfg, seed, std=0.08, gain_std=0.1, sharp=1.0, decisive_routing=False):
     """Normal weights; norm gains around zero; the mixing matrix of the heads near the identity; the projections of
-    queries and keys times ``sharp`` (peaked attention, so that a wrong key shows)."""
+    queries and keys times ``sharp`` (peaked attention, so that a wrong key shows).  ``decisive_routing``: the routers'
+    biases lie far apart and their matrices are small, so that no rounding of a router's input turns a choice."""
     rng = np.random.default_rng(seed)
     out = {}
     for name, shape in tensor_shapes(cfg).items():
@@ -144,8 +145,12 @@ def random_weights(cfg, seed, std=0.08, gain_std=0.1, sharp=1.0):
             w = 1.0 + rng.normal(0.0, gain_std, shape)
         elif tail == "talk":
             w = np.eye(shape[0]) + rng.normal(0.0, 0.15, shape)
+        elif name.endswith("router.b"):
+            w = rng.permutation(shape[0]) * 0.7 if decisive_routing else rng.normal(0.0, 0.3, shape)
+        elif name.endswith("mlp.router") and decisive_routing:
+            w = rng.normal(0.0, 0.02 * std, shape)
         elif tail == "b":
-            w = rng.normal(0.0, 0.3 if name.endswith("router.b") else std, shape)
+            w = rng.normal(0.0, std, shape)
         else:
             w = rng.normal(0.0, std, shape)
             if name.endswith((".mix.q", ".mix.uq", ".mix.k", ".mix.uk")):
@@ -177,17 +182,21 @@ def clamped_swish_ff(h, w_gate, w_up, w_down, limit, b_gate=None, b_up=None, b_d
     return (g * sigmoid(SWISH_ALPHA * g) * (u + 1.0)) @ w_down.T + (0.0 if b_down is None else b_down)
 
 
-def route(h, w_router, b_router, top):
-    """(chosen experts [n, top], their weights): the ``top`` largest logits, softmax over those alone."""
+def route(h, w_router, b_router, top, margins=None):
+    """(chosen experts [n, top], their weights): the ``top`` largest logits, softmax over those alone.  ``margins``
+    (a list) receives the smallest gap between a chosen logit and the best one left out."""
     z = h @ w_router.T + b_router
+    if margins is not None and top < z.shape[-1]:
+        ranked = -np.sort(-z, axis=-1)
+        margins.append(float((ranked[:, top - 1] - ranked[:, top]).min()))
     order = np.argsort(-z, axis=-1, kind="stable")[:, :top]
     zc = np.take_along_axis(z, order, axis=-1)
     e = np.exp(zc - zc.max(axis=-1, keepdims=True))
     return order, e / e.sum(axis=-1, keepdims=True)
 
 
-def routed_ff(h, weights, p, mlp):
-    ids, wts = route(h, weights[p + "router"], weights[p + "router.b"], mlp["router"]["top"])
+def routed_ff(h, weights, p, mlp, margins=None):
+    ids, wts = route(h, weights[p + "router"], weights[p + "router.b"], mlp["router"]["top"], margins)
     out = np.zeros_like(h)
     for t in range(h.shape[0]):
         for e, a in zip(ids[t], wts[t]):
@@ -200,11 +209,11 @@ def routed_ff(h, weights, p, mlp):
     return out
 
 
-def feed_forward(h, weights, p, mlp):
+def feed_forward(h, weights, p, mlp, margins=None):
     if mlp["kind"] == "dense":
         return clamped_swish_ff(h, weights[p + "gate"], weights[p + "up"], weights[p + "down"], mlp["limit"],
                                 weights[p + "gate.b"], weights[p + "up.b"], weights[p + "down.b"])
-    return routed_ff(h, weights, p, mlp)
+    return routed_ff(h, weights, p, mlp, margins)
 
 
 def head_slopes(H):
@@ -293,7 +302,7 @@ def run_order(cfg):
     return out + [(i, False) for i in range(b, n)]
 
 
-def forward(cfg, weights, ids, return_layers=False):
+def forward(cfg, weights, ids, return_layers=False, margins=None):
     """Logits [n, vocab] of one request's tokens, all at once."""
     eps, m = cfg["norm"]["eps"], cfg["residual_mult"]
     x0 = weights["embed"][np.asarray(ids)]
@@ -305,7 +314,18 @@ def forward(cfg, weights, ids, return_layers=False):
         layer, p = cfg["layers"][li], f"l{li}."
         x = x + m * MIXERS[layer["type"]](offset_norm(x, weights[p + "norm1"], eps), weights, p + "mix.", layer["mixer"], eps)
         if layer.get("mlp") is not None:
-            x = x + m * feed_forward(offset_norm(x, weights[p + "norm2"], eps), weights, p + "mlp.", layer["mlp"])
+            x = x + m * feed_forward(offset_norm(x, weights[p + "norm2"], eps), weights, p + "mlp.", layer["mlp"], margins)
         after.append(x.copy())
     logits = offset_norm(x, weights["final.norm"], eps) @ weights["embed"].T
     return (logits, np.stack(after)) if return_layers else logits
+
+
+def routing_margin(cfg, weights, ids):
+    """The smallest gap, over all routed layers and tokens, between a chosen router logit and the best one left out."""
+    margins = []
+    forward(cfg, weights, ids, margins=margins)
+    return min(margins) if margins else math.inf
+
+
+def greedy(logits):
+    return int(np.argmax(logits))

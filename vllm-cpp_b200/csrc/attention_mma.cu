@@ -1080,6 +1080,27 @@ VCB_EXPORT int vcb_attention_decode_mma_planes(const void* q, const void* cache,
 }
 
 // The same with shaped scores and an epilogue (see MmaAttnArgs): cap <= 0 no cap; bias_t, sink, gate null: none.
+VCB_EXPORT int vcb_attention_decode_mma_shaped_planes(const void* q, const void* cache, void* out, const int* q_start,
+                                               const int* ctx_lens, const int* block_table, int bt_stride,
+                                               const int* req_list, int n_list, int nsplit, float* part_o,
+                                               float* part_ml, int* counters, const int* split_tiles, int nh, int nkv,
+                                               int d, int page, int window, float scale, int num_pages, int* status,
+                                               int kv_share, float cap, const float* bias_t, int bias_len, const float* sink,
+                                               const void* gate, long long ldg, int precise_weights, int planes, void* stream) {
+    if (n_list <= 0) return 0;
+    int c = check_common(nh, nkv, d, page, window, num_pages);
+    if (c) return c;
+    if (kv_share < 1 || nkv % kv_share || (bias_t && bias_len <= 0) || (planes != 1 && planes != 2)) return VCB_ERR_BAD_ARG;
+    if (nsplit < 1 || nsplit > 32 || (nsplit > 1 && (!part_o || !part_ml || !counters))) return VCB_ERR_BAD_ARG;
+    MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
+                  block_table, req_list, nullptr, part_o, part_ml, counters, status, split_tiles, bt_stride, nh, nkv,
+                  page, window, scale, num_pages, planes, kv_share, cap, bias_t, bias_len, sink, (const __nv_bfloat16*)gate, ldg,
+                  precise_weights};
+    cudaStream_t s = (cudaStream_t)stream;
+    return d == 64 ? launch_decode<64>(a, n_list, nsplit, s) : launch_decode<128>(a, n_list, nsplit, s);
+}
+
+// Keys and values in planes of their own.
 VCB_EXPORT int vcb_attention_decode_mma_shaped(const void* q, const void* cache, void* out, const int* q_start,
                                                const int* ctx_lens, const int* block_table, int bt_stride,
                                                const int* req_list, int n_list, int nsplit, float* part_o,
@@ -1087,17 +1108,9 @@ VCB_EXPORT int vcb_attention_decode_mma_shaped(const void* q, const void* cache,
                                                int d, int page, int window, float scale, int num_pages, int* status,
                                                int kv_share, float cap, const float* bias_t, int bias_len, const float* sink,
                                                const void* gate, long long ldg, int precise_weights, void* stream) {
-    if (n_list <= 0) return 0;
-    int c = check_common(nh, nkv, d, page, window, num_pages);
-    if (c) return c;
-    if (kv_share < 1 || nkv % kv_share || (bias_t && bias_len <= 0)) return VCB_ERR_BAD_ARG;
-    if (nsplit < 1 || nsplit > 32 || (nsplit > 1 && (!part_o || !part_ml || !counters))) return VCB_ERR_BAD_ARG;
-    MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
-                  block_table, req_list, nullptr, part_o, part_ml, counters, status, split_tiles, bt_stride, nh, nkv,
-                  page, window, scale, num_pages, 2, kv_share, cap, bias_t, bias_len, sink, (const __nv_bfloat16*)gate, ldg,
-                  precise_weights};
-    cudaStream_t s = (cudaStream_t)stream;
-    return d == 64 ? launch_decode<64>(a, n_list, nsplit, s) : launch_decode<128>(a, n_list, nsplit, s);
+    return vcb_attention_decode_mma_shaped_planes(q, cache, out, q_start, ctx_lens, block_table, bt_stride, req_list, n_list, nsplit,
+                                                  part_o, part_ml, counters, split_tiles, nh, nkv, d, page, window, scale, num_pages,
+                                                  status, kv_share, cap, bias_t, bias_len, sink, gate, ldg, precise_weights, 2, stream);
 }
 
 VCB_EXPORT int vcb_attention_decode_mma(const void* q, const void* cache, void* out, const int* q_start,
@@ -1130,20 +1143,32 @@ VCB_EXPORT int vcb_attention_prefill_tc_planes(const void* q, const void* cache,
 }
 
 // The same with shaped scores and an epilogue (see MmaAttnArgs).
+VCB_EXPORT int vcb_attention_prefill_tc_shaped_planes(const void* q, const void* cache, void* out, const int* q_start,
+                                               const int* ctx_lens, const int* block_table, int bt_stride,
+                                               const int* tile_req, const int* tile_row0, int n_tiles, int nh,
+                                               int nkv, int d, int page, int window, float scale, int num_pages,
+                                               int* status, float cap, const float* bias_t, int bias_len, const float* sink,
+                                               const void* gate, long long ldg, int precise_weights, int planes, void* stream) {
+    if (n_tiles <= 0) return 0;
+    int c = check_common(nh, nkv, d, page, window, num_pages);
+    if (c) return c;
+    if ((bias_t && bias_len <= 0) || (planes != 1 && planes != 2)) return VCB_ERR_BAD_ARG;
+    MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
+                  block_table, tile_req, tile_row0, nullptr, nullptr, nullptr, status, nullptr, bt_stride, nh, nkv, page,
+                  window, scale, num_pages, planes, 1, cap, bias_t, bias_len, sink, (const __nv_bfloat16*)gate, ldg, precise_weights};
+    return d == 64 ? launch_prefill_tc<64>(a, n_tiles, (cudaStream_t)stream) : launch_prefill_tc<128>(a, n_tiles, (cudaStream_t)stream);
+}
+
+// Keys and values in planes of their own.
 VCB_EXPORT int vcb_attention_prefill_tc_shaped(const void* q, const void* cache, void* out, const int* q_start,
                                                const int* ctx_lens, const int* block_table, int bt_stride,
                                                const int* tile_req, const int* tile_row0, int n_tiles, int nh,
                                                int nkv, int d, int page, int window, float scale, int num_pages,
                                                int* status, float cap, const float* bias_t, int bias_len, const float* sink,
                                                const void* gate, long long ldg, int precise_weights, void* stream) {
-    if (n_tiles <= 0) return 0;
-    int c = check_common(nh, nkv, d, page, window, num_pages);
-    if (c) return c;
-    if (bias_t && bias_len <= 0) return VCB_ERR_BAD_ARG;
-    MmaAttnArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, q_start, ctx_lens,
-                  block_table, tile_req, tile_row0, nullptr, nullptr, nullptr, status, nullptr, bt_stride, nh, nkv, page,
-                  window, scale, num_pages, 2, 1, cap, bias_t, bias_len, sink, (const __nv_bfloat16*)gate, ldg, precise_weights};
-    return d == 64 ? launch_prefill_tc<64>(a, n_tiles, (cudaStream_t)stream) : launch_prefill_tc<128>(a, n_tiles, (cudaStream_t)stream);
+    return vcb_attention_prefill_tc_shaped_planes(q, cache, out, q_start, ctx_lens, block_table, bt_stride, tile_req, tile_row0, n_tiles,
+                                                  nh, nkv, d, page, window, scale, num_pages, status, cap, bias_t, bias_len, sink, gate,
+                                                  ldg, precise_weights, 2, stream);
 }
 
 VCB_EXPORT int vcb_attention_prefill_tc(const void* q, const void* cache, void* out, const int* q_start,

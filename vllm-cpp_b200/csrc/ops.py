@@ -63,6 +63,9 @@ _SIGNATURES = {
     "vcb_moe_combine_add": [_P, _P, _L, _P, _P, _P, _I, _I, _I, _P, _L, _I, _P],
     "vcb_attention_talking_mma": [_P, _P, _P, _P, _L, _P, _I, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
     "vcb_attention_talking": [_P, _P, _P, _P, _L, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _I, _P],
+    "vcb_attention_decode_mma_shaped_planes": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _I, _F, _P, _I,
+                                               _P, _P, _L, _I, _I, _P],
+    "vcb_attention_prefill_tc_shaped_planes": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _F, _P, _I, _P, _P, _L, _I, _I, _P],
     "vcb_attention_decode_mma_shaped": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _I, _F, _P, _I,
                                         _P, _P, _L, _I, _P],
     "vcb_attention_prefill_tc_shaped": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _F, _P, _I, _P, _P, _L, _I, _P],
@@ -340,10 +343,9 @@ def attention_decode_mma(q, cache, out, q_start, ctx_lens, block_table, req_list
         # ``precise_weights``: the softmax weights enter the P V product as two bfloat16 terms (16 bits of mantissa)
         # shaped scores: cap * tanh(scale * q.k / cap) + bias_t[head, min(distance, last)]; the epilogue: a sink logit per
         # head in the denominator, the head's output times sigmoid(head_gate[token, head]) (see attention_mma.cu)
-        _need(planes == 2, "attention_decode_mma: shaped scores come with keys and values in planes of their own")
         _need(bias_t is None or (bias_t.dim() == 2 and bias_t.shape[0] == num_heads), "attention_decode_mma: bias_t [heads, distances]")
         _epilogue_args(sink, head_gate, q.shape[0], num_heads, "attention_decode_mma")
-        _check(lib().vcb_attention_decode_mma_shaped(
+        _check(lib().vcb_attention_decode_mma_shaped_planes(
             _dev(q, "q"), _dev(cache, "cache"), _dev(out, "out"), _dev(q_start, "q_start", torch.int32),
             _dev(ctx_lens, "ctx_lens", torch.int32), _dev(block_table, "block_table", torch.int32),
             block_table.shape[1], None if req_list is None else _dev(req_list, "req_list", torch.int32),
@@ -354,7 +356,7 @@ def attention_decode_mma(q, cache, out, q_start, ctx_lens, block_table, req_list
             num_heads, num_kv_heads, head_dim, page_size, window, float(scale), cache.shape[0],
             status_tensor(q.device).data_ptr(), kv_share, float(cap),
             None if bias_t is None else _dev(bias_t, "bias_t", torch.float32), 0 if bias_t is None else bias_t.shape[1],
-            *_epilogue_ptrs(sink, head_gate), 1 if precise_weights else 0, _stream()), "attention_decode_mma")
+            *_epilogue_ptrs(sink, head_gate), 1 if precise_weights else 0, planes, _stream()), "attention_decode_mma")
         return
     _check(lib().vcb_attention_decode_mma_planes(
         _dev(q, "q"), _dev(cache, "cache"), _dev(out, "out"), _dev(q_start, "q_start", torch.int32),
@@ -398,16 +400,15 @@ def attention_prefill_tc(q, cache, out, q_start, ctx_lens, block_table, tile_req
     _need(tile_row0.numel() == n_tiles, "one first row per tile")
     _need(planes in (1, 2), "planes must be 1 or 2")
     if cap > 0 or bias_t is not None or sink is not None or head_gate is not None or precise_weights:
-        _need(planes == 2, "attention_prefill_tc: shaped scores come with keys and values in planes of their own")
         _need(bias_t is None or (bias_t.dim() == 2 and bias_t.shape[0] == num_heads), "attention_prefill_tc: bias_t [heads, distances]")
         _epilogue_args(sink, head_gate, q.shape[0], num_heads, "attention_prefill_tc")
-        _check(lib().vcb_attention_prefill_tc_shaped(
+        _check(lib().vcb_attention_prefill_tc_shaped_planes(
             _dev(q, "q"), _dev(cache, "cache"), _dev(out, "out"), _dev(q_start, "q_start", torch.int32),
             _dev(ctx_lens, "ctx_lens", torch.int32), _dev(block_table, "block_table", torch.int32),
             block_table.shape[1], _dev(tile_req, "tile_req", torch.int32), _dev(tile_row0, "tile_row0", torch.int32),
             n_tiles, num_heads, num_kv_heads, head_dim, page_size, window, float(scale), cache.shape[0],
             status_tensor(q.device).data_ptr(), float(cap), None if bias_t is None else _dev(bias_t, "bias_t", torch.float32),
-            0 if bias_t is None else bias_t.shape[1], *_epilogue_ptrs(sink, head_gate), 1 if precise_weights else 0, _stream()), "attention_prefill_tc")
+            0 if bias_t is None else bias_t.shape[1], *_epilogue_ptrs(sink, head_gate), 1 if precise_weights else 0, planes, _stream()), "attention_prefill_tc")
         return
     _check(lib().vcb_attention_prefill_tc_planes(
         _dev(q, "q"), _dev(cache, "cache"), _dev(out, "out"), _dev(q_start, "q_start", torch.int32),

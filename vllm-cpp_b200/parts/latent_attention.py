@@ -25,6 +25,7 @@ import torch
 
 from ..config.model_spec import PartSpec
 from ..csrc import ops
+from . import position as _position  # noqa: F401  (registers the position encodings)
 from .attention import PagedAttentionKernels
 from .base import POSITION_ENCODINGS, PagedKVSpec, ParamSpec, build_part, register_mixer, workspace_piece
 
@@ -161,6 +162,10 @@ class RotaryLatentAttention(PagedAttentionKernels):
         self.w_in = self.w_uq = self.w_qn = self.w_c = self.w_qk = self.w_uv = self.w_o = None
 
     # -- tensors
+    def score_shaping(self):
+        # attention weights are wanted in 32-bit: the tensor-core kernels take them as two bfloat16 terms
+        return {"precise_weights": True}
+
     def gate_rows(self) -> int:
         return {"head": self.heads, "channel": self.heads * self.vd, "none": 0}[self.gate]
 

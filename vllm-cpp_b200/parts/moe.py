@@ -28,6 +28,7 @@ from typing import Dict
 import torch
 
 from ..csrc import ops
+from . import mlp as _mlp  # noqa: F401  (registers the feed-forwards a shared expert may be)
 from .base import FEED_FORWARDS, FeedForward, ParamSpec, build_part, register_feed_forward, workspace_piece
 
 
