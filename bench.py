@@ -1239,6 +1239,190 @@ def lutodra_attention_kernels(z, peaks, add, rnd):
     return []
 
 
+# ------------------------------------------------------------------- the Gipinex design beside Lutodra's attention layers
+# Layer sizes that resemble real models'.  Gipinex: latent attention (queries through a latent, one rotated key part, a cached
+# row of kv_rank + rot_dim = 128) with a dense clamped feed-forward and with routed experts beside a shared expert, then
+# two layers of attention with talking heads and a distance bias with routed experts; the first two layers are walked twice.
+# Lutodra with attention layers alone (head norms, rotation, a sink, a gate per head; dense and routed feed-forwards; the
+# same loop) at equal width, heads, head size, feed-forward widths and experts is the nearest model the engine has.
+GIPINEX_SIZES = {"1k": dict(width=1024, heads=8, kv_heads=2, dim=128, ff=4096, experts=8, top=2, expert_ff=1024, layers=4, q_rank=384),
+                 "2k": dict(width=2048, heads=16, kv_heads=4, dim=128, ff=8192, experts=16, top=2, expert_ff=2048, layers=4, q_rank=768)}
+GIPINEX_VOCAB, GIPINEX_CONTEXT, GIPINEX_PROMPT, GIPINEX_RANK, GIPINEX_ROT = 32000, 2048, 2048, 96, 32
+
+
+def gipinex_configs(size):
+    z = GIPINEX_SIZES[size]
+    w, h, d = z["width"], z["heads"], z["dim"]
+    dense = {"kind": "dense", "ff": z["ff"], "limit": 7.0}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"], "limit": 7.0}, "router": {"experts": z["experts"], "top": z["top"]},
+           "shared": {"ff": z["expert_ff"], "limit": 7.0}}
+    lat = {"heads": h, "dim": d - GIPINEX_ROT, "rot_dim": GIPINEX_ROT, "vdim": d, "kv_rank": GIPINEX_RANK, "q_rank": z["q_rank"],
+           "scale": d ** -0.5, "rot": {"base": 1e6, "dims": GIPINEX_ROT}}
+    att = {"heads": h, "kv_heads": z["kv_heads"], "dim": d, "vdim": d, "scale": 0.125}
+    layers = [{"type": "latent_attention", "mixer": lat, "mlp": dense}, {"type": "latent_attention", "mixer": lat, "mlp": moe},
+              {"type": "attention", "mixer": att, "mlp": moe}, {"type": "attention", "mixer": att, "mlp": moe}]
+    loop = {"start": 0, "stop": 2, "times": 2}
+    gipinex = {"architecture": "Gipinex", "vocab": GIPINEX_VOCAB, "width": w, "norm": {"eps": 1e-6}, "residual_mult": 0.7,
+               "loop": loop, "layers": [layers[i % 4] for i in range(z["layers"])]}
+    l_moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"], "scale": 2.5}}
+    l_att = {"heads": h, "kv_heads": z["kv_heads"], "dim": d, "vdim": d, "scale": d ** -0.5, "rot": {"base": 1e6, "dims": d // 2}}
+    lutodra = {"architecture": "Lutodra", "vocab": GIPINEX_VOCAB, "width": w, "norm": {"eps": 1e-6}, "loop": loop,
+               "layers": [{"type": "attention", "mixer": l_att, "mlp": {"kind": "dense", "ff": z["ff"]} if i % 4 == 0 else l_moe}
+                          for i in range(z["layers"])]}
+    return gipinex, lutodra
+
+
+def run_gipinex(a) -> int:
+    """Prefill and decode throughput of the Gipinex design beside Lutodra's attention layers at equal layer sizes (random
+    weights, synthetic cache contents), and the design's own kernels alone beside the like kernels of the engine's other
+    models with their share of the measured peaks.  One JSON line."""
+    import numpy as np
+    peaks = load_peaks()
+    steps, warmup = max(1, a.steps), max(3, a.warmup)
+    rng = np.random.default_rng(0)
+    sampler = ClockSampler()
+    sampler.start()
+    sampler.mark("decode")
+    out = {"metric": "prefill and decode tok/s of Gipinex beside Lutodra's attention layers at equal layer sizes (bf16, random weights)",
+           "n_gpus": 1, "steps": steps, "warmup": warmup, "dtype": "bf16", "data": "synthetic", "sizes": {}, "peaks": peaks}
+    sizes = a.gipinex.split(",") if a.gipinex != "all" else sorted(GIPINEX_SIZES)
+    for size in sizes:
+        gipinex, lutodra = gipinex_configs(size)
+        args = (steps, warmup, rng, peaks, GIPINEX_VOCAB, GIPINEX_CONTEXT, GIPINEX_PROMPT)
+        out["sizes"][size] = {"layers": GIPINEX_SIZES[size], "gipinex": measure_design(gipinex, (8, 64), *args),
+                              "lutodra_attention": measure_design(lutodra, (8, 64), *args)}
+    if not a.skip_points:
+        out["kernels"] = gipinex_kernels(GIPINEX_SIZES[sizes[-1]], peaks)
+    out["clocks"] = sampler.stop()
+    big = out["sizes"][sizes[-1]]
+    out.update(value=big["gipinex"]["decode"]["8"]["tok_s"], unit=f"tokens/s (Gipinex, {sizes[-1]}-wide layers, batch 8)",
+               higher_is_better=True, gpu_launches=big["gipinex"]["decode"]["8"]["launches_per_step"] * steps,
+               config={"sizes": GIPINEX_SIZES, "context": GIPINEX_CONTEXT, "prompt": GIPINEX_PROMPT, "kv_rank": GIPINEX_RANK,
+                       "rot_dim": GIPINEX_ROT, "l2": "a step's weights exceed the 126 MB of L2"})
+    print(json.dumps(out))
+    return 0
+
+
+def gipinex_kernels(z, peaks):
+    """The design's own kernels alone at one layer size, each beside the like kernel of another model of the engine:
+    [{kernel, like, us, GB/s or TFLOP/s, share of the measured peak}, ...] (CUDA graphs on rotating buffers)."""
+    import numpy as np
+    import torch
+    from vllm_cpp_b200.csrc import ops
+    from vllm_cpp_b200.engine.runner import HostStep
+    from vllm_cpp_b200.parts.attention import PagedAttention
+    from vllm_cpp_b200.config.model_spec import PartSpec
+    from vllm_cpp_b200.parts.talking_attention import TalkingHeadsAttention, distance_slopes
+    h, nh, nkv, d, page, bf, dev = z["width"], z["heads"], z["kv_heads"], z["dim"], 16, torch.bfloat16, "cuda"
+    rank, rot, ff = GIPINEX_RANK, GIPINEX_ROT, z["ff"]
+    rows = []
+
+    def rnd(*shape, dtype=bf, scale=1.0):
+        return (torch.randn(*shape, device=dev) * scale).to(dtype)
+
+    def add(name, like, fn, copies, bytes_=0, flops=0):
+        us = ops.time_in_graph(fn, reps=max(4, copies))
+        rate = bytes_ / us / 1e3 if bytes_ else flops / us / 1e6
+        rows.append({"kernel": name, "like": like, "us": round(us, 2), ("gb_s" if bytes_ else "tflop_s"): round(rate, 1),
+                     "of_peak": round(rate / (peaks["hbm_gbs"] if bytes_ else peaks["bf16_tflops"]), 4)})
+
+    talk = TalkingHeadsAttention(h, nh, nkv, d, 0.125, 1e-6, bf, dev)
+    mix = (torch.eye(nh, device=dev) + 0.1 * torch.randn(nh, nh, device=dev)).contiguous()
+    slopes = torch.from_numpy(distance_slopes(nh, 8.0).astype(np.float32)).to(dev)
+    plainatt = PagedAttention(h, nh, nkv, d, True, False, 0, PartSpec("none"), bf, dev)
+    # ---- a prompt
+    t = GIPINEX_PROMPT
+    n_pages = t // page + 2
+    bt = torch.arange(n_pages, dtype=torch.int32, device=dev).view(1, -1)
+    q_start, ctx = torch.tensor([0, t], dtype=torch.int32, device=dev), torch.zeros(1, dtype=torch.int32, device=dev)
+    q, o, gate = rnd(t, nh * d), torch.empty(t, nh * d, dtype=bf, device=dev), rnd(t, nh * d)
+    kv = rnd(n_pages, 2 * nkv * page * d, scale=0.5)
+    host = HostStep([t], [0], page)
+    items = torch.from_numpy(talk.step_arrays()[talk._items_key()](host)).to(dev)
+    seen = t * (t + 1) // 2
+    add(f"attention with talking heads, distance bias, gate and two-term weights, prompt of {t}", "", lambda i: ops.attention_talking_mma(
+        q, kv, o, gate, items, items.shape[0], q_start, ctx, bt, mix, slopes, nsplit=1, n_reqs=1, num_heads=nh, num_kv_heads=nkv, head_dim=d,
+        page_size=page, window=0, scale=0.125), 4, flops=4.0 * nh * d * seen)
+    G = nh // nkv
+    n_tiles = -(-t * G // ops.TC_ATTENTION_TILE_ROWS)
+    tile_req = torch.zeros(n_tiles, dtype=torch.int32, device=dev)
+    tile_row0 = torch.from_numpy((np.arange(n_tiles, dtype=np.int32) * ops.TC_ATTENTION_TILE_ROWS)[::-1].copy()).to(dev)
+    kv4 = kv.view(n_pages, 2, nkv, page * d)
+    hg = rnd(t, nh)
+    add(f"Lutodra: attention with sink, head gate and two-term weights, prompt of {t}", "like the one above", lambda i: ops.attention_prefill_tc(
+        q, kv4, o, q_start, ctx, bt, tile_req, tile_row0, num_heads=nh, num_kv_heads=nkv, head_dim=d, page_size=page, window=0, scale=d ** -0.5,
+        sink=slopes, head_gate=hg, precise_weights=True), 4, flops=4.0 * nh * d * seen)
+    # ---- single tokens
+    for batch in (8, 64):
+        contexts = [GIPINEX_CONTEXT - 1] * batch
+        blocks = -(-GIPINEX_CONTEXT // page)
+        bt = torch.arange(batch * blocks, dtype=torch.int32, device=dev).view(batch, blocks)
+        q_start, ctx = torch.arange(batch + 1, dtype=torch.int32, device=dev), torch.tensor(contexts, dtype=torch.int32, device=dev)
+        host = HostStep([1] * batch, contexts, page)
+        items = torch.from_numpy(talk.step_arrays()[talk._items_key()](host)).to(dev)
+        runs = host.shapes[talk._items_key() + "_runs"]
+        po, pml = torch.empty(batch * runs * nh * d, device=dev), torch.empty(batch * runs * nh * 2, device=dev)
+        q, o, gate = rnd(batch, nh * d), torch.empty(batch, nh * d, dtype=bf, device=dev), rnd(batch, nh * d)
+        kv = rnd(batch * blocks + 1, 2 * nkv * page * d, scale=0.5)
+        moved = batch * GIPINEX_CONTEXT * 2 * nkv * d * 2
+        add(f"attention with talking heads, decode, batch {batch}, context {GIPINEX_CONTEXT} ({runs} runs of keys a request)", "",
+            lambda i: ops.attention_talking_mma(q, kv, o, gate, items, items.shape[0], q_start, ctx, bt, mix, slopes, nsplit=runs, n_reqs=batch,
+                                                num_heads=nh, num_kv_heads=nkv, head_dim=d, page_size=page, window=0, scale=0.125,
+                                                part_o=po, part_ml=pml), 4, bytes_=moved)
+        host = HostStep([1] * batch, contexts, page)
+        split_tiles = torch.from_numpy(plainatt.step_arrays()[plainatt._splits_key()](host)).to(dev)
+        nsplit = host.shapes[plainatt._splits_key()]
+        share = ops.decode_head_groups(nh, nkv)
+        need = batch * nh * nsplit
+        p2, pm2, tickets = torch.empty(need * d, device=dev), torch.empty(need * 2, device=dev), torch.zeros(batch * nkv * share, dtype=torch.int32, device=dev)
+        hg = rnd(batch, nh)
+        add(f"Lutodra: attention with sink, head gate and two-term weights, decode, batch {batch}, context {GIPINEX_CONTEXT}", "like the one above",
+            lambda i: ops.attention_decode_mma(q, kv.view(-1, 2, nkv, page * d), o, q_start, ctx, bt, None, batch, nsplit, p2, pm2, tickets,
+                                               num_heads=nh, num_kv_heads=nkv * share, head_dim=d, page_size=page, window=0, scale=d ** -0.5,
+                                               split_tiles=split_tiles, kv_share=share, sink=slopes, head_gate=hg, precise_weights=True), 4,
+            bytes_=moved)
+    # ---- rows: the latent's norm, the shared key part's rotation and the cache write; the queries' latent norm; the activation
+    inv_freq = torch.from_numpy(np.power(1e6, -2.0 * np.arange(rot // 2) / rot).astype(np.float32)).to(dev)
+    ones_d = torch.ones(d, device=dev)
+    for t in (64, 2048):
+        c = 6 if t == 64 else 3
+        n_pages = t // page + 1
+        pos = torch.arange(t, dtype=torch.int32, device=dev)
+        rot_ = torch.zeros(t, dtype=torch.int32, device=dev)
+        bt = torch.arange(n_pages, dtype=torch.int32, device=dev).view(1, -1)
+        raw, qq = [rnd(t, rank + rot) for _ in range(c)], [rnd(t, nh * d) for _ in range(c)]
+        cache1 = rnd(n_pages, page * (rank + rot))
+        gain = torch.ones(rank, device=dev)
+        add(f"latent norm + rotation of the shared key part and of {nh} query parts + cache write, {t} tokens", "", lambda i: ops.latent_rope_cache_write(
+            raw[i % c], gain, qq[i % c], inv_freq, pos, rot_, bt, cache1, rank=rank, num_heads=nh, q_stride=d, q_off=d - rot, pairing=1,
+            page_size=page, eps=1e-6), c, bytes_=t * ((rank + rot) * 4 + nh * rot * 4))
+        proj = [rnd(t, (nh + 2 * nkv) * d) for _ in range(c)]
+        qo = [torch.empty(t, nh * d, dtype=bf, device=dev) for _ in range(c)]
+        cache2 = rnd(n_pages, 2 * nkv * page * d)
+        add(f"q/k divided by their root mean square per head + cache write of both planes, {t} tokens", "Lutodra's kernel (there with rotation)",
+            lambda i: ops.qk_head_rope_cache_write(proj[i % c], 0, nh * d, nh * d, ones_d, ones_d, None, qo[i % c], cache2, pos, rot_, bt,
+                                                   num_heads=nh, num_kv_heads=nkv, head_dim=d, v_head_dim=d, row=d, page_size=page, eps=1e-6,
+                                                   write_kv=True), c, bytes_=t * (nh + nkv) * d * 4 + t * nkv * d * 2)
+        cq, cqo = [rnd(t, z["q_rank"]) for _ in range(c)], [torch.empty(t, z["q_rank"], dtype=bf, device=dev) for _ in range(c)]
+        gq = torch.ones(z["q_rank"], device=dev)
+        add(f"norm of the queries' latent ({z['q_rank']} wide), {t} tokens", "", lambda i: ops.rows_rmsnorm(cq[i % c], gq, cqo[i % c], 1e-6), c,
+            bytes_=t * z["q_rank"] * 4)
+        gu, act = [rnd(t, 2 * ff) for _ in range(c)], [torch.empty(t, ff, dtype=bf, device=dev) for _ in range(c)]
+        bias = rnd(2 * ff, dtype=torch.float32, scale=0.1)
+        add(f"clamped activation with biases, width {ff}, {t} tokens", "", lambda i: ops.clamped_swish_mul(gu[i % c], bias, act[i % c], limit=7.0, alpha=1.702), c,
+            bytes_=t * ff * 6)
+        add(f"Qwen2: silu(gate) * up, width {ff}, {t} tokens", "like the one above", lambda i: ops.silu_mul(gu[i % c], act[i % c]), c, bytes_=t * ff * 6)
+        x = [rnd(t, h, dtype=torch.float32) for _ in range(c)]
+        dl, pair = [rnd(t, h) for _ in range(c)], [torch.empty(t, 2 * h, dtype=bf, device=dev) for _ in range(c)]
+        add(f"stream + 0.7 * addition into the left half of the re-making product's input, {t} tokens", "", lambda i: ops.cast_rows(
+            x[i % c], dl[i % c], 0.7, pair[i % c][:, :h]), c, bytes_=t * h * 8)
+        nrm, gh = [torch.empty(t, h, dtype=bf, device=dev) for _ in range(c)], torch.ones(h, device=dev)
+        add(f"stream += 0.7 * addition, then the norm, {t} tokens", "the kernel Qwen2 runs with factor 1", lambda i: ops.add_rmsnorm(
+            x[i % c], dl[i % c], gh, nrm[i % c], 1e-6, None, 0.7), c, bytes_=t * h * 12)
+    ops.check_status()
+    return rows
+
+
 # ------------------------------------------------------------------------------------------ reference arm
 REFERENCE_NOTES = ("the reference's own faults at these sizes, none of which changes the work of a step: an untied lm_head is "
                    "copied over the embedding table (src/model/qwen.cpp:279-281); the bias area of 3*1024 floats a layer "
@@ -1393,6 +1577,10 @@ def main() -> int:
     ap.add_argument("--lutodra", default="", metavar="SIZES",
                     help="instead of the benchmark's workload: prefill and decode throughput of the Lutodra design beside Retodra "
                          "at equal layer sizes, and the design's kernels alone: 'all' or a comma list of " + ",".join(sorted(LUTODRA_SIZES)))
+    ap.add_argument("--gipinex", default="", metavar="SIZES",
+                    help="instead of the benchmark's workload: prefill and decode throughput of the Gipinex design beside Lutodra's "
+                         "attention layers at equal layer sizes, and the design's kernels alone: 'all' or a comma list of "
+                         + ",".join(sorted(GIPINEX_SIZES)))
     ap.add_argument("--retodra", default="", metavar="SIZES",
                     help="instead of the benchmark's workload: prefill and decode throughput of the Retodra design beside Qwen2 "
                          f"at equal layer sizes ({','.join(sorted(RETODRA_SIZES))} or 'all'), and the design's kernels alone "
@@ -1434,6 +1622,8 @@ def main() -> int:
         return run_retodra(a)
     if a.lutodra:
         return run_lutodra(a)
+    if a.gipinex:
+        return run_gipinex(a)
     if a.mix:
         return run_mix(cfg, a)
     if a.kernels:
