@@ -163,7 +163,6 @@ VCB_EXPORT int vcb_attention_talking(const void* q, const void* cache, void* out
 // ------------------------------------------------------------------ tensor cores (bfloat16, heads of 64 or 128)
 #define TKM_ROWS 16            // query rows of a work item
 #define TKM_KEYS 32            // keys of a tile
-#define TKM_RAW_LD 40          // floats between two rows of the raw scores in shared memory (conflict-free 64-bit accesses)
 #define TKM_MAX_HEADS 16       // a warp per head, and a head's fragments want more registers than 1024 threads leave
 #define TKM_ITEM_INTS 6        // request, first row within the request's rows of this step, rows, first key, end of keys, partial slot or -1
 
@@ -197,17 +196,28 @@ __device__ __forceinline__ uint32_t tkm_pack(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-// The part of x that its bfloat16 rounding leaves out, so that hi + lo carries 16 bits of x's mantissa.
-__device__ __forceinline__ float tkm_rest(float x) { return x - __bfloat162float(__float2bfloat16_rn(x)); }
+// Two weights (not negative) as two pairs of bfloat16: hi is the upper half of each float (cut off, so that what is left
+// is exact), lo the rounding of what is left: hi + lo carries 16 bits of the weight's mantissa.
+__device__ __forceinline__ void tkm_two_terms(float x, float y, uint32_t& hi, uint32_t& lo) {
+    const uint32_t bx = __float_as_uint(x), by = __float_as_uint(y);
+    hi = __byte_perm(bx, by, 0x7632);
+    lo = tkm_pack(x - __uint_as_float(bx & 0xffff0000u), y - __uint_as_float(by & 0xffff0000u));
+}
+
+__device__ __forceinline__ float tkm_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 
 template <int D, int MAXT>
 __global__ void __launch_bounds__(MAXT) attention_talking_mma_kernel(TalkingMmaArgs a) {
     constexpr int LDK = D + 8;                      // bfloat16 elements between two keys of a tile in shared memory
     extern __shared__ __align__(16) unsigned char tkm_smem[];
-    __nv_bfloat16* ks = reinterpret_cast<__nv_bfloat16*>(tkm_smem);                 // [G][TKM_KEYS][LDK] normed keys
-    __nv_bfloat16* vs = ks + (size_t)a.G * TKM_KEYS * LDK;                          // [G][TKM_KEYS][LDK] values
-    float* raw = reinterpret_cast<float*>(vs + (size_t)a.G * TKM_KEYS * LDK);      // [H][TKM_ROWS][TKM_RAW_LD]
-    float* mixs = raw + (size_t)a.H * TKM_ROWS * TKM_RAW_LD;                        // [H][H]
+    __nv_bfloat16* ks = reinterpret_cast<__nv_bfloat16*>(tkm_smem);                 // [2][G][TKM_KEYS][LDK] normed keys, two stages
+    __nv_bfloat16* vs = ks + 2 * (size_t)a.G * TKM_KEYS * LDK;                      // [2][G][TKM_KEYS][LDK] values
+    float* raw0 = reinterpret_cast<float*>(vs + 2 * (size_t)a.G * TKM_KEYS * LDK); // [2][H][key octet][lane] float4, taking turns
+    float* mixs = raw0 + 2 * (size_t)a.H * TKM_ROWS * TKM_KEYS;                     // [H][H]
     pdl_start();
     const int h = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gr = lane >> 2, tq = lane & 3;        // fragment row (and row + 8) and column pair of this lane
@@ -244,36 +254,65 @@ __global__ void __launch_bounds__(MAXT) attention_talking_mma_kernel(TalkingMmaA
     const size_t block = (size_t)a.page * D;
     const size_t page_elems = 2 * (size_t)a.G * block;
     constexpr int CH = D / 8;                       // 16-byte chunks of a key
-    const int n_chunks = a.G * TKM_KEYS * CH;
-
-    for (int k0 = k_lo; k0 < k_hi; k0 += TKM_KEYS) {
-        __syncthreads();                            // the tile before is read no more (and mixs is in place)
-        // the tile's keys and values of every kv head, out of their pages into rows of LDK elements
-        for (int c = threadIdx.x; c < n_chunks; c += blockDim.x) {
-            const int gk = c / (TKM_KEYS * CH), rem = c - gk * (TKM_KEYS * CH);
-            const int key = rem / CH, ch = rem - key * CH;
-            const int j = k0 + key;
-            uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
+    constexpr int PER = CH / 4;                     // chunks a thread copies of a key: four threads share one
+    const size_t stage_elems = (size_t)a.G * TKM_KEYS * LDK;
+    const int n_pairs = a.G * TKM_KEYS;
+    // a tile's keys and values of every kv head, out of their pages into rows of LDK elements of stage `st`: asynchronous
+    // 16-byte copies, a page looked up once per (kv head, key) by the four threads that share the key
+    auto fetch = [&](int st, int k0) {
+        __nv_bfloat16* kd = ks + (size_t)st * stage_elems;
+        __nv_bfloat16* vd = vs + (size_t)st * stage_elems;
+        for (int p = threadIdx.x >> 2; p < n_pairs; p += blockDim.x >> 2) {
+            const int gk = p / TKM_KEYS, key = p - gk * TKM_KEYS, j = k0 + key, sub = threadIdx.x & 3;
+            const __nv_bfloat16* src = a.cache;
+            uint32_t bytes = 0;
+            int sl = 0;
             if (j < k_hi) {
-                const int lp = j / a.page, sl = j - lp * a.page;
+                const int lp = j / a.page;
+                sl = j - lp * a.page;
                 const int pg = lp < a.bt_stride ? bt[lp] : -1;
                 if ((unsigned)pg >= (unsigned)a.num_pages) {
                     if (a.status) atomicCAS(a.status, 0, VCB_STATUS_BAD_PAGE);
                 } else {
-                    const __nv_bfloat16* src = a.cache + (size_t)pg * page_elems + (size_t)gk * block + kv_pos(ch * 8, sl, D, a.page, 2);
-                    kv = *reinterpret_cast<const uint4*>(src);
-                    vv = *reinterpret_cast<const uint4*>(src + (size_t)a.G * block);
+                    src = a.cache + (size_t)pg * page_elems + (size_t)gk * block;
+                    bytes = 16;
                 }
             }
-            *reinterpret_cast<uint4*>(ks + ((size_t)gk * TKM_KEYS + key) * LDK + ch * 8) = kv;
-            *reinterpret_cast<uint4*>(vs + ((size_t)gk * TKM_KEYS + key) * LDK + ch * 8) = vv;
+#pragma unroll
+            for (int e = 0; e < PER; ++e) {
+                const int ch = sub * PER + e;
+                const __nv_bfloat16* from = bytes ? src + kv_pos(ch * 8, sl, D, a.page, 2) : a.cache;
+                const uint32_t to_k = cx_smem(kd + ((size_t)gk * TKM_KEYS + key) * LDK + ch * 8);
+                const uint32_t to_v = cx_smem(vd + ((size_t)gk * TKM_KEYS + key) * LDK + ch * 8);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(to_k), "l"(from), "r"(bytes) : "memory");
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(to_v), "l"(bytes ? from + (size_t)a.G * block : from), "r"(bytes)
+                             : "memory");
+            }
         }
-        __syncthreads();
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    };
+
+    float off[TKM_KEYS / 4];                        // slope * (a key's offset from this lane's first key of the tile)
+#pragma unroll
+    for (int n = 0; n < TKM_KEYS / 8; ++n) {
+        off[2 * n] = slope * (float)(n * 8);
+        off[2 * n + 1] = slope * (float)(n * 8 + 1);
+    }
+    if (k_lo < k_hi) fetch(0, k_lo);
+    int it = 0;
+    for (int k0 = k_lo; k0 < k_hi; k0 += TKM_KEYS, ++it) {
+        const int st = it & 1;
+        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        __syncthreads();                            // the tile has arrived; the round before is over for every warp (and mixs is in place)
+        if (k0 + TKM_KEYS < k_hi) fetch(st ^ 1, k0 + TKM_KEYS);        // the next tile travels while this one is worked on
+        const __nv_bfloat16* kst = ks + (size_t)st * stage_elems;
+        const __nv_bfloat16* vst = vs + (size_t)st * stage_elems;
+        float* raw = raw0 + (size_t)st * a.H * TKM_ROWS * TKM_KEYS;
         // raw scores of this warp's head: 16 rows x 32 keys
         float sc[TKM_KEYS / 8][4];
 #pragma unroll
         for (int n = 0; n < TKM_KEYS / 8; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.0f;
-        const __nv_bfloat16* kh = ks + (size_t)g * TKM_KEYS * LDK;
+        const __nv_bfloat16* kh = kst + (size_t)g * TKM_KEYS * LDK;
 #pragma unroll
         for (int s = 0; s < D / 16; ++s) {
 #pragma unroll
@@ -282,65 +321,71 @@ __global__ void __launch_bounds__(MAXT) attention_talking_mma_kernel(TalkingMmaA
                 tkm_mma(sc[n], qf[s], *reinterpret_cast<const uint32_t*>(kp), *reinterpret_cast<const uint32_t*>(kp + 8));
             }
         }
-        // scale, distance bias, and into shared memory for the other heads (a key no row sees, or beyond the item: 0)
-        float* mine = raw + (size_t)h * TKM_ROWS * TKM_RAW_LD;
+        // scale, distance bias (slope * (position - key), the key's offset inside the tile taken from constants), and into
+        // shared memory for the other heads, a lane's four values of a key octet side by side
+        const float base_a = -slope * (float)(pos_a - k0 - tq * 2), base_b = base_a - slope * 8.0f;
+        float4* mine = reinterpret_cast<float4*>(raw) + (size_t)h * (TKM_KEYS / 8) * 32 + lane;
 #pragma unroll
-        for (int n = 0; n < TKM_KEYS / 8; ++n) {
-            const int j = k0 + n * 8 + tq * 2;
-            float2 ra, rb;
-            ra.x = sc[n][0] * a.scale - slope * (float)(pos_a - j);
-            ra.y = sc[n][1] * a.scale - slope * (float)(pos_a - j - 1);
-            rb.x = sc[n][2] * a.scale - slope * (float)(pos_b - j);
-            rb.y = sc[n][3] * a.scale - slope * (float)(pos_b - j - 1);
-            *reinterpret_cast<float2*>(mine + gr * TKM_RAW_LD + n * 8 + tq * 2) = ra;
-            *reinterpret_cast<float2*>(mine + (gr + 8) * TKM_RAW_LD + n * 8 + tq * 2) = rb;
-        }
+        for (int n = 0; n < TKM_KEYS / 8; ++n)
+            mine[n * 32] = make_float4(fmaf(sc[n][0], a.scale, base_a + off[2 * n]), fmaf(sc[n][1], a.scale, base_a + off[2 * n + 1]),
+                                       fmaf(sc[n][2], a.scale, base_b + off[2 * n]), fmaf(sc[n][3], a.scale, base_b + off[2 * n + 1]));
         __syncthreads();
-        // this head's mixed scores, in the fragments' places
+        // this head's mixed scores, in the fragments' places, in units of log 2 (the exponentials below are powers of two)
 #pragma unroll
         for (int n = 0; n < TKM_KEYS / 8; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.0f;
         for (int gg = 0; gg < a.H; ++gg) {
-            const float w = mixs[h * a.H + gg];
-            const float* theirs = raw + (size_t)gg * TKM_ROWS * TKM_RAW_LD;
+            const float w = mixs[h * a.H + gg] * 1.4426950408889634f;
+            const float4* theirs = reinterpret_cast<const float4*>(raw) + (size_t)gg * (TKM_KEYS / 8) * 32 + lane;
 #pragma unroll
             for (int n = 0; n < TKM_KEYS / 8; ++n) {
-                const float2 ra = *reinterpret_cast<const float2*>(theirs + gr * TKM_RAW_LD + n * 8 + tq * 2);
-                const float2 rb = *reinterpret_cast<const float2*>(theirs + (gr + 8) * TKM_RAW_LD + n * 8 + tq * 2);
-                sc[n][0] = fmaf(w, ra.x, sc[n][0]);
-                sc[n][1] = fmaf(w, ra.y, sc[n][1]);
-                sc[n][2] = fmaf(w, rb.x, sc[n][2]);
-                sc[n][3] = fmaf(w, rb.y, sc[n][3]);
+                const float4 r = theirs[n * 32];
+                sc[n][0] = fmaf(w, r.x, sc[n][0]);
+                sc[n][1] = fmaf(w, r.y, sc[n][1]);
+                sc[n][2] = fmaf(w, r.z, sc[n][2]);
+                sc[n][3] = fmaf(w, r.w, sc[n][3]);
             }
         }
-        // what a row may see: keys up to its own position (and inside its window), below the item's end
+        // (the next round writes the other copy of raw, and the round after that starts behind a barrier)
+        // what a row may see: keys up to its own position (and inside its window), below the item's end.  A tile that lies
+        // wholly before the item's first row, inside the item's keys, is seen by every row
+        const bool all_seen = a.window <= 0 && k0 + TKM_KEYS - 1 <= pos0 && k0 + TKM_KEYS <= k_hi;
         float mx_a = -INFINITY, mx_b = -INFINITY;
+        if (all_seen) {
 #pragma unroll
-        for (int n = 0; n < TKM_KEYS / 8; ++n) {
+            for (int n = 0; n < TKM_KEYS / 8; ++n) {
+                mx_a = fmaxf(mx_a, fmaxf(sc[n][0], sc[n][1]));
+                mx_b = fmaxf(mx_b, fmaxf(sc[n][2], sc[n][3]));
+            }
+        } else {
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int j = k0 + n * 8 + tq * 2 + e;
-                const bool in = j < k_hi;
-                const bool see_a = in && row_a && j <= pos_a && (a.window <= 0 || pos_a - j < a.window);
-                const bool see_b = in && row_b && j <= pos_b && (a.window <= 0 || pos_b - j < a.window);
-                if (!see_a) sc[n][e] = -INFINITY;
-                if (!see_b) sc[n][2 + e] = -INFINITY;
-                mx_a = fmaxf(mx_a, sc[n][e]);
-                mx_b = fmaxf(mx_b, sc[n][2 + e]);
+            for (int n = 0; n < TKM_KEYS / 8; ++n) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int j = k0 + n * 8 + tq * 2 + e;
+                    const bool in = j < k_hi;
+                    const bool see_a = in && row_a && j <= pos_a && (a.window <= 0 || pos_a - j < a.window);
+                    const bool see_b = in && row_b && j <= pos_b && (a.window <= 0 || pos_b - j < a.window);
+                    if (!see_a) sc[n][e] = -INFINITY;
+                    if (!see_b) sc[n][2 + e] = -INFINITY;
+                    mx_a = fmaxf(mx_a, sc[n][e]);
+                    mx_b = fmaxf(mx_b, sc[n][2 + e]);
+                }
             }
         }
         mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
         mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
         mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
         mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+        // a row that has seen nothing yet keeps the reference 0, so that no difference of infinities is taken
         const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
-        const float ca = mn_a == -INFINITY ? 1.0f : expf(m_a - mn_a), cb = mn_b == -INFINITY ? 1.0f : expf(m_b - mn_b);
+        const float ra = mn_a == -INFINITY ? 0.0f : mn_a, rb = mn_b == -INFINITY ? 0.0f : mn_b;
+        const float ca = tkm_exp2(m_a - ra), cb = tkm_exp2(m_b - rb);            // 2^(-inf) = 0 for a row's first keys
         float sum_a = 0.0f, sum_b = 0.0f;
 #pragma unroll
         for (int n = 0; n < TKM_KEYS / 8; ++n) {
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-                const float pa = sc[n][e] == -INFINITY ? 0.0f : expf(sc[n][e] - mn_a);
-                const float pb = sc[n][2 + e] == -INFINITY ? 0.0f : expf(sc[n][2 + e] - mn_b);
+                const float pa = tkm_exp2(sc[n][e] - ra), pb = tkm_exp2(sc[n][2 + e] - rb);
                 sc[n][e] = pa;
                 sc[n][2 + e] = pb;
                 sum_a += pa;
@@ -357,19 +402,16 @@ __global__ void __launch_bounds__(MAXT) attention_talking_mma_kernel(TalkingMmaA
         m_b = mn_b;
 #pragma unroll
         for (int n = 0; n < D / 8; ++n) { o[n][0] *= ca; o[n][1] *= ca; o[n][2] *= cb; o[n][3] *= cb; }
-        // weights x values: the weights as A fragments in two bfloat16 terms, the values' tile read transposed
-        const __nv_bfloat16* vh = vs + (size_t)g * TKM_KEYS * LDK;
+        // weights x values: the weights as A fragments in two bfloat16 terms (the upper half of the float, and what that
+        // leaves, rounded), the values' tile read transposed
+        const __nv_bfloat16* vh = vst + (size_t)g * TKM_KEYS * LDK;
 #pragma unroll
         for (int s = 0; s < TKM_KEYS / 16; ++s) {
             uint32_t hi[4], lo[4];
-            hi[0] = tkm_pack(sc[2 * s][0], sc[2 * s][1]);
-            hi[1] = tkm_pack(sc[2 * s][2], sc[2 * s][3]);
-            hi[2] = tkm_pack(sc[2 * s + 1][0], sc[2 * s + 1][1]);
-            hi[3] = tkm_pack(sc[2 * s + 1][2], sc[2 * s + 1][3]);
-            lo[0] = tkm_pack(tkm_rest(sc[2 * s][0]), tkm_rest(sc[2 * s][1]));
-            lo[1] = tkm_pack(tkm_rest(sc[2 * s][2]), tkm_rest(sc[2 * s][3]));
-            lo[2] = tkm_pack(tkm_rest(sc[2 * s + 1][0]), tkm_rest(sc[2 * s + 1][1]));
-            lo[3] = tkm_pack(tkm_rest(sc[2 * s + 1][2]), tkm_rest(sc[2 * s + 1][3]));
+            tkm_two_terms(sc[2 * s][0], sc[2 * s][1], hi[0], lo[0]);
+            tkm_two_terms(sc[2 * s][2], sc[2 * s][3], hi[1], lo[1]);
+            tkm_two_terms(sc[2 * s + 1][0], sc[2 * s + 1][1], hi[2], lo[2]);
+            tkm_two_terms(sc[2 * s + 1][2], sc[2 * s + 1][3], hi[3], lo[3]);
             const uint32_t vrow = cx_smem(vh + (size_t)(s * 16 + (lane & 15)) * LDK);
 #pragma unroll
             for (int n = 0; n < D / 8; ++n) {
@@ -414,7 +456,7 @@ __global__ void __launch_bounds__(MAXT) attention_talking_mma_kernel(TalkingMmaA
     }
 }
 
-// Joins the partial sums of single-row items: request r's row was cut into `nsplit` runs of keys, whose partials lie
+// Joins the partial sums of single-row items (their references are in units of log 2): request r's row was cut into `nsplit` runs of keys, whose partials lie
 // in slots r * nsplit .. r * nsplit + nsplit - 1.  A CTA per request, a warp per head.
 __global__ void attention_talking_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gate, long long ldg,
@@ -427,7 +469,7 @@ __global__ void attention_talking_merge_kernel(const float* __restrict__ part_o,
     float l = 0.0f;
     for (int s = 0; s < nsplit; ++s) {
         const float* ml = part_ml + (((size_t)r * nsplit + s) * H + h) * 2;
-        if (ml[0] != -INFINITY) l += ml[1] * expf(ml[0] - m);
+        if (ml[0] != -INFINITY) l += ml[1] * exp2f(ml[0] - m);
     }
     const int row = q_start[r];
     const float inv = l > 0.0f ? 1.0f / l : 0.0f;
@@ -436,7 +478,7 @@ __global__ void attention_talking_merge_kernel(const float* __restrict__ part_o,
         for (int s = 0; s < nsplit; ++s) {
             const size_t at = ((size_t)r * nsplit + s) * H + h;
             const float ms = part_ml[at * 2];
-            if (ms != -INFINITY) acc = fmaf(part_o[at * D + i], expf(ms - m), acc);
+            if (ms != -INFINITY) acc = fmaf(part_o[at * D + i], exp2f(ms - m), acc);
         }
         float y = acc * inv;
         if (gate) y *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)row * ldg + (size_t)h * D + i])));
@@ -445,7 +487,7 @@ __global__ void attention_talking_merge_kernel(const float* __restrict__ part_o,
 }
 
 VCB_EXPORT long long vcb_attention_talking_mma_smem(int H, int G, int D) {
-    return (long long)2 * G * TKM_KEYS * (D + 8) * 2 + (long long)H * TKM_ROWS * TKM_RAW_LD * 4 + (long long)H * H * 4;
+    return (long long)4 * G * TKM_KEYS * (D + 8) * 2 + (long long)2 * H * TKM_ROWS * TKM_KEYS * 4 + (long long)H * H * 4;
 }
 
 // items: [n_items, 6] as TalkingMmaArgs says.  nsplit > 1: every item is one row of a request cut into nsplit runs

@@ -1481,6 +1481,16 @@ TALKING_MAX_SPLITS = 32
 TALKING_ITEM_INTS = 6
 
 
+def talking_mma_fits(num_heads: int, num_kv_heads: int, head_dim: int) -> bool:
+    """True if the tensor-core kernel of attention_talking takes these sizes: its shared memory holds two stages of every
+    kv head's key and value tiles and two copies of all heads' raw scores of a tile (the same sum as in
+    csrc/attention_talking.cu, vcb_attention_talking_mma_smem)."""
+    if head_dim not in TALKING_MMA_HEAD_DIMS or num_heads > TALKING_MMA_MAX_HEADS:
+        return False
+    smem = 4 * num_kv_heads * TALKING_KEY_TILE * (head_dim + 8) * 2 + 2 * num_heads * TALKING_ITEM_ROWS * TALKING_KEY_TILE * 4 + num_heads * num_heads * 4
+    return smem <= 220 * 1024
+
+
 def attention_talking_mma(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor], items: torch.Tensor,
                           n_items: int, q_start, ctx_lens, block_table, mix: torch.Tensor, slope: Optional[torch.Tensor], *,
                           nsplit: int, n_reqs: int, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int,

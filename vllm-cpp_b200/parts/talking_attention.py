@@ -75,7 +75,7 @@ class TalkingHeadsAttention(Mixer):
 
     # -- the tensor-core kernel's work lists
     def _tensor_core_path(self) -> bool:
-        return (self.dtype == torch.bfloat16 and self.d in ops.TALKING_MMA_HEAD_DIMS and self.nh <= ops.TALKING_MMA_MAX_HEADS)
+        return self.dtype == torch.bfloat16 and ops.talking_mma_fits(self.nh, self.nkv, self.d)
 
     def _items_key(self) -> str:
         return f"talk_items_w{self.window}"
