@@ -1368,7 +1368,7 @@ def gipinex_kernels(z, peaks):
         add(f"attention with talking heads, decode, batch {batch}, context {GIPINEX_CONTEXT} ({runs} runs of keys a request)", "",
             lambda i: ops.attention_talking_mma(q, kv, o, gate, items, items.shape[0], q_start, ctx, bt, mix, slopes, nsplit=runs, n_reqs=batch,
                                                 num_heads=nh, num_kv_heads=nkv, head_dim=d, page_size=page, window=0, scale=0.125,
-                                                part_o=po, part_ml=pml), 4, bytes_=moved)
+                                                part_o=po, part_ml=pml, single_rows=True), 4, bytes_=moved)
         host = HostStep([1] * batch, contexts, page)
         split_tiles = torch.from_numpy(plainatt.step_arrays()[plainatt._splits_key()](host)).to(dev)
         nsplit = host.shapes[plainatt._splits_key()]

@@ -456,6 +456,262 @@ __global__ void __launch_bounds__(MAXT) attention_talking_mma_kernel(TalkingMmaA
     }
 }
 
+// ------------------------------------------------------------------ single tokens on tensor cores
+// A request that brings one token: the fragment's 16 rows are the heads of one kv head's group instead of 16 tokens, so the
+// keys of a kv head are multiplied once for all its heads.  A CTA per work item (a request and a run of its keys, as
+// above), a warp per (kv head, sixteenth-of-a-tile): warp (g, ks) takes keys ks * 16 .. + 16 of every tile of 16 * KS keys
+// for the heads of group g, with sums of its own that the CTA joins at the end.  Raw scores of all heads meet in shared
+// memory as before; a warp mixes the rows of its own heads.
+template <int D, int MAXT>
+__global__ void __launch_bounds__(MAXT) attention_talking_decode_kernel(TalkingMmaArgs a, int KS) {
+    constexpr int LDK = D + 8;
+    extern __shared__ __align__(16) unsigned char tkm_smem[];
+    const int tile = 16 * KS;
+    const size_t stage_elems = (size_t)a.G * tile * LDK;
+    __nv_bfloat16* ks_ = reinterpret_cast<__nv_bfloat16*>(tkm_smem);               // [2][G][tile][LDK]
+    __nv_bfloat16* vs_ = ks_ + 2 * stage_elems;                                     // [2][G][tile][LDK]
+    float* raw0 = reinterpret_cast<float*>(vs_ + 2 * stage_elems);                 // [2][H][tile]
+    float* mixs = raw0 + 2 * (size_t)a.H * tile;                                    // [H][H], times log2(e)
+    pdl_start();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = warp / KS, ks = warp - g * KS;
+    const int gr = lane >> 2, tq = lane & 3;
+    const int Hg = a.H / a.G;
+    const int* item = a.items + (size_t)blockIdx.x * TKM_ITEM_INTS;
+    const int req = item[0], k_lo = item[3], k_hi = item[4], slot_out = item[5];
+    const int row = a.q_start[req] + item[1];
+    const int pos = a.ctx_lens[req] + item[1];
+    const int* bt = a.block_table + (size_t)req * a.bt_stride;
+    for (int i = threadIdx.x; i < a.H * a.H; i += blockDim.x) mixs[i] = a.mix[i] * 1.4426950408889634f;
+    const bool row_a = gr < Hg, row_b = gr + 8 < Hg;
+    const int head_a = g * Hg + gr, head_b = head_a + 8;
+    const float slope_a = (a.slope && row_a) ? a.slope[head_a] : 0.0f, slope_b = (a.slope && row_b) ? a.slope[head_b] : 0.0f;
+
+    uint32_t qf[D / 16][4];
+    {
+        const __nv_bfloat16* qa = a.q + ((size_t)row * a.H + head_a) * D + tq * 2;
+        const __nv_bfloat16* qb = qa + (size_t)8 * D;
+#pragma unroll
+        for (int s = 0; s < D / 16; ++s) {
+            qf[s][0] = row_a ? *reinterpret_cast<const uint32_t*>(qa + s * 16) : 0u;
+            qf[s][1] = row_b ? *reinterpret_cast<const uint32_t*>(qb + s * 16) : 0u;
+            qf[s][2] = row_a ? *reinterpret_cast<const uint32_t*>(qa + s * 16 + 8) : 0u;
+            qf[s][3] = row_b ? *reinterpret_cast<const uint32_t*>(qb + s * 16 + 8) : 0u;
+        }
+    }
+    float o[D / 8][4];
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.0f, l_b = 0.0f;
+
+    const size_t block = (size_t)a.page * D;
+    const size_t page_elems = 2 * (size_t)a.G * block;
+    constexpr int CH = D / 8, PER = CH / 4;
+    const int n_pairs = a.G * tile;
+    auto fetch = [&](int st, int k0) {
+        __nv_bfloat16* kd = ks_ + (size_t)st * stage_elems;
+        __nv_bfloat16* vd = vs_ + (size_t)st * stage_elems;
+        for (int p = threadIdx.x >> 2; p < n_pairs; p += blockDim.x >> 2) {
+            const int gk = p / tile, key = p - gk * tile, j = k0 + key, sub = threadIdx.x & 3;
+            const __nv_bfloat16* src = a.cache;
+            uint32_t bytes = 0;
+            int sl = 0;
+            if (j < k_hi) {
+                const int lp = j / a.page;
+                sl = j - lp * a.page;
+                const int pg = lp < a.bt_stride ? bt[lp] : -1;
+                if ((unsigned)pg >= (unsigned)a.num_pages) {
+                    if (a.status) atomicCAS(a.status, 0, VCB_STATUS_BAD_PAGE);
+                } else {
+                    src = a.cache + (size_t)pg * page_elems + (size_t)gk * block;
+                    bytes = 16;
+                }
+            }
+#pragma unroll
+            for (int e = 0; e < PER; ++e) {
+                const int ch = sub * PER + e;
+                const __nv_bfloat16* from = bytes ? src + kv_pos(ch * 8, sl, D, a.page, 2) : a.cache;
+                const uint32_t to_k = cx_smem(kd + ((size_t)gk * tile + key) * LDK + ch * 8);
+                const uint32_t to_v = cx_smem(vd + ((size_t)gk * tile + key) * LDK + ch * 8);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(to_k), "l"(from), "r"(bytes) : "memory");
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(to_v), "l"(bytes ? from + (size_t)a.G * block : from), "r"(bytes)
+                             : "memory");
+            }
+        }
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    };
+
+    if (k_lo < k_hi) fetch(0, k_lo);
+    int it = 0;
+    for (int k0 = k_lo; k0 < k_hi; k0 += tile, ++it) {
+        const int st = it & 1;
+        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        __syncthreads();
+        if (k0 + tile < k_hi) fetch(st ^ 1, k0 + tile);
+        const __nv_bfloat16* kh = ks_ + (size_t)st * stage_elems + ((size_t)g * tile + ks * 16) * LDK;
+        const __nv_bfloat16* vh = vs_ + (size_t)st * stage_elems + ((size_t)g * tile + ks * 16) * LDK;
+        float* raw = raw0 + (size_t)st * a.H * tile;
+        float sc[2][4];
+#pragma unroll
+        for (int n = 0; n < 2; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.0f;
+#pragma unroll
+        for (int s = 0; s < D / 16; ++s) {
+#pragma unroll
+            for (int n = 0; n < 2; ++n) {
+                const __nv_bfloat16* kp = kh + (size_t)(n * 8 + gr) * LDK + s * 16 + tq * 2;
+                tkm_mma(sc[n], qf[s], *reinterpret_cast<const uint32_t*>(kp), *reinterpret_cast<const uint32_t*>(kp + 8));
+            }
+        }
+        // scale and distance bias; the rows of this group's heads into shared memory
+        const int j0 = k0 + ks * 16 + tq * 2;           // this lane's first key of the tile
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            const float da = (float)(pos - j0 - n * 8);
+            if (row_a) *reinterpret_cast<float2*>(raw + (size_t)head_a * tile + ks * 16 + n * 8 + tq * 2) =
+                make_float2(fmaf(sc[n][0], a.scale, -slope_a * da), fmaf(sc[n][1], a.scale, -slope_a * (da - 1.0f)));
+            if (row_b) *reinterpret_cast<float2*>(raw + (size_t)head_b * tile + ks * 16 + n * 8 + tq * 2) =
+                make_float2(fmaf(sc[n][2], a.scale, -slope_b * da), fmaf(sc[n][3], a.scale, -slope_b * (da - 1.0f)));
+        }
+        __syncthreads();
+        // the mixed scores of this warp's heads at its sixteen keys, in units of log 2
+#pragma unroll
+        for (int n = 0; n < 2; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.0f;
+        const float* wa = mixs + (size_t)(row_a ? head_a : 0) * a.H;
+        const float* wb = mixs + (size_t)(row_b ? head_b : 0) * a.H;
+        for (int gg = 0; gg < a.H; ++gg) {
+            const float ua = wa[gg], ub = wb[gg];
+            const float* theirs = raw + (size_t)gg * tile + ks * 16 + tq * 2;
+#pragma unroll
+            for (int n = 0; n < 2; ++n) {
+                const float2 r = *reinterpret_cast<const float2*>(theirs + n * 8);
+                sc[n][0] = fmaf(ua, r.x, sc[n][0]);
+                sc[n][1] = fmaf(ua, r.y, sc[n][1]);
+                sc[n][2] = fmaf(ub, r.x, sc[n][2]);
+                sc[n][3] = fmaf(ub, r.y, sc[n][3]);
+            }
+        }
+        float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int j = j0 + n * 8 + e;
+                const bool see = j < k_hi && j <= pos && (a.window <= 0 || pos - j < a.window);
+                if (!(see && row_a)) sc[n][e] = -INFINITY;
+                if (!(see && row_b)) sc[n][2 + e] = -INFINITY;
+                mx_a = fmaxf(mx_a, sc[n][e]);
+                mx_b = fmaxf(mx_b, sc[n][2 + e]);
+            }
+        }
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+        const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+        const float ra = mn_a == -INFINITY ? 0.0f : mn_a, rb = mn_b == -INFINITY ? 0.0f : mn_b;
+        const float ca = tkm_exp2(m_a - ra), cb = tkm_exp2(m_b - rb);
+        float sum_a = 0.0f, sum_b = 0.0f;
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const float pa = tkm_exp2(sc[n][e] - ra), pb = tkm_exp2(sc[n][2 + e] - rb);
+                sc[n][e] = pa;
+                sc[n][2 + e] = pb;
+                sum_a += pa;
+                sum_b += pb;
+            }
+        }
+        sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 1);
+        sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 2);
+        sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 1);
+        sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 2);
+        l_a = l_a * ca + sum_a;
+        l_b = l_b * cb + sum_b;
+        m_a = mn_a;
+        m_b = mn_b;
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n) { o[n][0] *= ca; o[n][1] *= ca; o[n][2] *= cb; o[n][3] *= cb; }
+        uint32_t hi[4], lo[4];
+        tkm_two_terms(sc[0][0], sc[0][1], hi[0], lo[0]);
+        tkm_two_terms(sc[0][2], sc[0][3], hi[1], lo[1]);
+        tkm_two_terms(sc[1][0], sc[1][1], hi[2], lo[2]);
+        tkm_two_terms(sc[1][2], sc[1][3], hi[3], lo[3]);
+        const uint32_t vrow = cx_smem(vh + (size_t)(lane & 15) * LDK);
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n) {
+            uint32_t b0, b1;
+            asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(b0), "=r"(b1) : "r"(vrow + n * 16));
+            tkm_mma(o[n], hi, b0, b1);
+            tkm_mma(o[n], lo, b0, b1);
+        }
+    }
+    // the warps' sums meet in shared memory (where the tiles lay): [warp][16 rows][D] and [warp][16][2]
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    __syncthreads();
+    float* jo = reinterpret_cast<float*>(tkm_smem);
+    float* jml = jo + (size_t)(blockDim.x >> 5) * 16 * D;
+    {
+        float* mine = jo + (size_t)warp * 16 * D;
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n) {
+            *reinterpret_cast<float2*>(mine + (size_t)gr * D + n * 8 + tq * 2) = make_float2(o[n][0], o[n][1]);
+            *reinterpret_cast<float2*>(mine + (size_t)(gr + 8) * D + n * 8 + tq * 2) = make_float2(o[n][2], o[n][3]);
+        }
+        if (tq == 0) {
+            jml[((size_t)warp * 16 + gr) * 2] = m_a;
+            jml[((size_t)warp * 16 + gr) * 2 + 1] = l_a;
+            jml[((size_t)warp * 16 + gr + 8) * 2] = m_b;
+            jml[((size_t)warp * 16 + gr + 8) * 2 + 1] = l_b;
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < a.H * D; idx += blockDim.x) {
+        const int head = idx / D, i = idx - head * D;
+        const int gh = head / Hg, r = head - gh * Hg;
+        float m = -INFINITY;
+        for (int s = 0; s < KS; ++s) m = fmaxf(m, jml[((size_t)(gh * KS + s) * 16 + r) * 2]);
+        float l = 0.0f, acc = 0.0f;
+        for (int s = 0; s < KS; ++s) {
+            const size_t at = (size_t)(gh * KS + s) * 16 + r;
+            const float ms = jml[at * 2];
+            if (ms == -INFINITY) continue;
+            const float f = tkm_exp2(ms - m);
+            l = fmaf(jml[at * 2 + 1], f, l);
+            acc = fmaf(jo[at * D + i], f, acc);
+        }
+        if (slot_out >= 0) {
+            a.part_o[((size_t)slot_out * a.H + head) * D + i] = acc;
+            if (i == 0) {
+                a.part_ml[((size_t)slot_out * a.H + head) * 2] = m;
+                a.part_ml[((size_t)slot_out * a.H + head) * 2 + 1] = l;
+            }
+        } else {
+            float y = l > 0.0f ? acc / l : 0.0f;
+            if (a.gate) y *= 1.0f / (1.0f + expf(-__bfloat162float(a.gate[(size_t)row * a.ldg + (size_t)head * D + i])));
+            a.out[((size_t)row * a.H + head) * D + i] = __float2bfloat16_rn(y);
+        }
+    }
+}
+
+// Sixteenths of a tile that the single-token kernel's CTA takes at once (a warp each per kv head), 0: the sizes do not fit.
+static int tkm_decode_split(int H, int G, int D, long long* smem_out) {
+    if (H % G || H / G > 16 || (D != 64 && D != 128)) return 0;
+    const int most_warps = D == 128 ? 8 : 16;
+    for (int KS = 4; KS >= 1; KS >>= 1) {
+        if (G * KS > most_warps) continue;
+        const long long tiles = (long long)4 * G * 16 * KS * (D + 8) * 2, join = (long long)G * KS * 16 * (D + 2) * 4;
+        const long long smem = (tiles > join ? tiles : join) + (long long)2 * H * 16 * KS * 4 + (long long)H * H * 4;
+        if (smem <= 200 * 1024) { *smem_out = smem; return KS; }
+    }
+    return 0;
+}
+
+VCB_EXPORT int vcb_attention_talking_decode_fits(int H, int G, int D) {
+    long long smem = 0;
+    return tkm_decode_split(H, G, D, &smem);
+}
+
 // Joins the partial sums of single-row items (their references are in units of log 2): request r's row was cut into `nsplit` runs of keys, whose partials lie
 // in slots r * nsplit .. r * nsplit + nsplit - 1.  A CTA per request, a warp per head.
 __global__ void attention_talking_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
@@ -491,12 +747,13 @@ VCB_EXPORT long long vcb_attention_talking_mma_smem(int H, int G, int D) {
 }
 
 // items: [n_items, 6] as TalkingMmaArgs says.  nsplit > 1: every item is one row of a request cut into nsplit runs
-// (slot = request * nsplit + run), and the merge kernel writes the n_reqs rows.
+// (slot = request * nsplit + run), and the merge kernel writes the n_reqs rows.  single_rows 1: every item is one row
+// (a step of single tokens), which the kernel whose fragment rows are heads takes where its tiles fit.
 VCB_EXPORT int vcb_attention_talking_mma(const void* q, const void* cache, void* out, const void* gate, long long ldg,
                                          const int* items, int n_items, const int* q_start, const int* ctx_lens,
                                          const int* block_table, int bt_stride, const float* mix, const float* slope,
                                          float* part_o, float* part_ml, int nsplit, int n_reqs, int H, int G, int D, int page,
-                                         int window, float scale, int num_pages, int* status, void* stream) {
+                                         int window, float scale, int num_pages, int* status, int single_rows, void* stream) {
     if (n_items <= 0) return 0;
     if (!q || !cache || !out || !items || !mix || H <= 0 || G <= 0 || H % G || page <= 0 || window < 0 || num_pages < 0 || nsplit < 1)
         return VCB_ERR_BAD_ARG;
@@ -507,6 +764,24 @@ VCB_EXPORT int vcb_attention_talking_mma(const void* q, const void* cache, void*
     TalkingMmaArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, (const __nv_bfloat16*)gate, ldg, items,
                      q_start, ctx_lens, block_table, mix, slope, part_o, part_ml, bt_stride, H, G, page, window, num_pages, scale, status};
     cudaStream_t s = (cudaStream_t)stream;
+    long long dsmem = 0;
+    const int KS = single_rows ? tkm_decode_split(H, G, D, &dsmem) : 0;
+    if (KS) {
+        static unsigned long long ddone[2] = {0, 0};
+        if (D == 64) {
+            const int e = vcb_allow_dynamic_smem(attention_talking_decode_kernel<64, 512>, 200 * 1024, &ddone[0]);
+            if (e) return e;
+            vcb_launch(attention_talking_decode_kernel<64, 512>, n_items, G * KS * 32, (size_t)dsmem, s, a, KS);
+        } else {
+            const int e = vcb_allow_dynamic_smem(attention_talking_decode_kernel<128, 256>, 200 * 1024, &ddone[1]);
+            if (e) return e;
+            vcb_launch(attention_talking_decode_kernel<128, 256>, n_items, G * KS * 32, (size_t)dsmem, s, a, KS);
+        }
+        if (nsplit > 1)
+            vcb_launch(attention_talking_merge_kernel, n_reqs, H * 32, 0, s, (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out,
+                       (const __nv_bfloat16*)gate, ldg, q_start, H, D, nsplit);
+        return vcb_last_error();
+    }
     static unsigned long long done[4] = {0, 0, 0, 0};
 #define TKM_GO(DD, TT, I)                                                                                   \
     do {                                                                                                    \

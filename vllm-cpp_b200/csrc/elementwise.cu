@@ -259,10 +259,46 @@ __global__ void cast_rows_kernel(const float* __restrict__ x, const T* __restric
     }
 }
 
+// bfloat16 rows of a multiple of 8 columns, 16-byte aligned: eight elements a thread.
+__global__ void cast_rows_bf16x8_kernel(const float* __restrict__ x, const __nv_bfloat16* __restrict__ delta, float mult,
+                                        __nv_bfloat16* __restrict__ out, int width, long long ldo, long long n_vec) {
+    pdl_start();
+    const long long vpr = width >> 3;
+    for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < n_vec; v += (long long)gridDim.x * blockDim.x) {
+        const long long t = v / vpr;
+        const int i = (int)(v - t * vpr) << 3;
+        const float4 a = *reinterpret_cast<const float4*>(x + t * width + i), b = *reinterpret_cast<const float4*>(x + t * width + i + 4);
+        float f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        if (delta) {
+            const uint4 d4 = *reinterpret_cast<const uint4*>(delta + t * width + i);
+            const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&d4);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 d = __bfloat1622float2(d2[e]);
+                f[2 * e] = fmaf(mult, d.x, f[2 * e]);
+                f[2 * e + 1] = fmaf(mult, d.y, f[2 * e + 1]);
+            }
+        }
+        uint4 o4;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
+        *reinterpret_cast<uint4*>(out + t * ldo + i) = o4;
+    }
+}
+
 VCB_EXPORT int vcb_cast_rows(const float* x, const void* delta, float mult, void* out, int n, int width, long long ldo, int dtype,
                              void* stream) {
     if (n <= 0 || width <= 0) return 0;
     if (!x || !out || ldo < width) return VCB_ERR_BAD_ARG;
+    if (dtype == VCB_BF16 && width % 8 == 0 && ldo % 8 == 0 && !(((uintptr_t)x | (uintptr_t)delta | (uintptr_t)out) & 15)) {
+        const long long n_vec = (long long)n * (width >> 3);
+        long long vb = (n_vec + 255) / 256;
+        if (vb > (long long)vcb_sm_count() * 16) vb = (long long)vcb_sm_count() * 16;
+        vcb_launch(cast_rows_bf16x8_kernel, (int)vb, 256, 0, (cudaStream_t)stream, x, (const __nv_bfloat16*)delta, mult, (__nv_bfloat16*)out,
+                   width, ldo, n_vec);
+        return vcb_last_error();
+    }
     const long long total = (long long)n * width;
     long long blocks = (total + 255) / 256;
     if (blocks > (long long)vcb_sm_count() * 16) blocks = (long long)vcb_sm_count() * 16;
@@ -383,34 +419,57 @@ __global__ void clamped_swish_mul_kernel(const T* __restrict__ gu, const float* 
     }
 }
 
-// bfloat16 rows of a multiple of 8 columns: 16 bytes of gate and of up a thread.
+// bfloat16 rows of a multiple of 8 columns: 16 bytes of gate and of up per vector, four vectors a thread and round so
+// that eight loads are in flight before the first is used.  The result is rounded to bfloat16, so the exponential and
+// the division are the fast ones (a few units in the last place of a float), as in silu_mul_bf16x8_kernel; the 32-bit
+// path above uses expf and a true division.
 __global__ void clamped_swish_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, const float* __restrict__ bias,
                                                 __nv_bfloat16* __restrict__ out, int inter, long long n_vec, float limit,
                                                 float alpha, float up_shift) {
     pdl_start();
+    constexpr int U = 4;
     const long long vpr = inter >> 3;
-    for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < n_vec; v += (long long)gridDim.x * blockDim.x) {
-        const long long t = v / vpr;
-        const int i = (int)(v - t * vpr) << 3;
-        const __nv_bfloat16* row = gu + (size_t)t * 2 * inter;
-        const uint4 g4 = *reinterpret_cast<const uint4*>(row + i), u4 = *reinterpret_cast<const uint4*>(row + inter + i);
-        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
-        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
-        uint4 o4;
-        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+    const long long stride = (long long)gridDim.x * blockDim.x * U;
+    for (long long v0 = (long long)blockIdx.x * blockDim.x * U + threadIdx.x; v0 < n_vec; v0 += stride) {
+        uint4 g4[U], u4[U];
+        long long dst[U];
+        int col[U];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            float2 a = __bfloat1622float2(g2[e]), b = __bfloat1622float2(u2[e]);
-            if (bias) {
-                a.x += bias[i + 2 * e]; a.y += bias[i + 2 * e + 1];
-                b.x += bias[inter + i + 2 * e]; b.y += bias[inter + i + 2 * e + 1];
-            }
-            a.x = fminf(a.x, limit); a.y = fminf(a.y, limit);
-            b.x = fminf(fmaxf(b.x, -limit), limit); b.y = fminf(fmaxf(b.y, -limit), limit);
-            o2[e] = __floats2bfloat162_rn(a.x * (1.0f / (1.0f + expf(-alpha * a.x))) * (b.x + up_shift),
-                                          a.y * (1.0f / (1.0f + expf(-alpha * a.y))) * (b.y + up_shift));
+        for (int k = 0; k < U; ++k) {
+            const long long v = v0 + (long long)k * blockDim.x;
+            if (v >= n_vec) { dst[k] = -1; col[k] = 0; g4[k] = u4[k] = make_uint4(0, 0, 0, 0); continue; }
+            const long long t = v / vpr;
+            col[k] = (int)(v - t * vpr) << 3;
+            const __nv_bfloat16* row = gu + (size_t)t * 2 * inter;
+            g4[k] = *reinterpret_cast<const uint4*>(row + col[k]);
+            u4[k] = *reinterpret_cast<const uint4*>(row + inter + col[k]);
+            dst[k] = t * inter + col[k];
         }
-        *reinterpret_cast<uint4*>(out + (size_t)t * inter + i) = o4;
+#pragma unroll
+        for (int k = 0; k < U; ++k) {
+            if (dst[k] < 0) continue;
+            const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4[k]);
+            const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4[k]);
+            float bg[8], bu[8];
+            if (bias) {
+                *reinterpret_cast<float4*>(bg) = *reinterpret_cast<const float4*>(bias + col[k]);
+                *reinterpret_cast<float4*>(bg + 4) = *reinterpret_cast<const float4*>(bias + col[k] + 4);
+                *reinterpret_cast<float4*>(bu) = *reinterpret_cast<const float4*>(bias + inter + col[k]);
+                *reinterpret_cast<float4*>(bu + 4) = *reinterpret_cast<const float4*>(bias + inter + col[k] + 4);
+            }
+            uint4 o4;
+            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float2 a = __bfloat1622float2(g2[e]), b = __bfloat1622float2(u2[e]);
+                if (bias) { a.x += bg[2 * e]; a.y += bg[2 * e + 1]; b.x += bu[2 * e]; b.y += bu[2 * e + 1]; }
+                a.x = fminf(a.x, limit); a.y = fminf(a.y, limit);
+                b.x = fminf(fmaxf(b.x, -limit), limit); b.y = fminf(fmaxf(b.y, -limit), limit);
+                o2[e] = __floats2bfloat162_rn(__fdividef(a.x, 1.0f + __expf(-alpha * a.x)) * (b.x + up_shift),
+                                              __fdividef(a.y, 1.0f + __expf(-alpha * a.y)) * (b.y + up_shift));
+            }
+            *reinterpret_cast<uint4*>(out + dst[k]) = o4;
+        }
     }
 }
 
@@ -419,9 +478,9 @@ VCB_EXPORT int vcb_clamped_swish_mul(const void* gu, const float* bias, void* ou
     if (n_tokens <= 0) return 0;
     if (inter <= 0 || !(limit > 0.0f)) return VCB_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == VCB_BF16 && inter % 8 == 0 && ((((uintptr_t)gu | (uintptr_t)out) & 15) == 0)) {
+    if (dtype == VCB_BF16 && inter % 8 == 0 && ((((uintptr_t)gu | (uintptr_t)out | (uintptr_t)bias) & 15) == 0)) {
         const long long n_vec = (long long)n_tokens * (inter >> 3);
-        long long blocks = (n_vec + 255) / 256;
+        long long blocks = (n_vec + 1023) / 1024;
         if (blocks > (long long)vcb_sm_count() * 16) blocks = (long long)vcb_sm_count() * 16;
         vcb_launch(clamped_swish_mul_bf16x8_kernel, (int)blocks, 256, 0, s, (const __nv_bfloat16*)gu, bias, (__nv_bfloat16*)out,
                    inter, n_vec, limit, alpha, up_shift);

@@ -61,7 +61,7 @@ _SIGNATURES = {
     "vcb_clamped_swish_mul": [_P, _P, _P, _I, _I, _F, _F, _F, _I, _P],
     "vcb_moe_router_biased": [_P, _L, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P],
     "vcb_moe_combine_add": [_P, _P, _L, _P, _P, _P, _I, _I, _I, _P, _L, _I, _P],
-    "vcb_attention_talking_mma": [_P, _P, _P, _P, _L, _P, _I, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
+    "vcb_attention_talking_mma": [_P, _P, _P, _P, _L, _P, _I, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _I, _P],
     "vcb_attention_talking": [_P, _P, _P, _P, _L, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _I, _P],
     "vcb_attention_decode_mma_shaped_planes": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _I, _F, _P, _I,
                                                _P, _P, _L, _I, _I, _P],
@@ -1494,11 +1494,14 @@ def talking_mma_fits(num_heads: int, num_kv_heads: int, head_dim: int) -> bool:
 def attention_talking_mma(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor], items: torch.Tensor,
                           n_items: int, q_start, ctx_lens, block_table, mix: torch.Tensor, slope: Optional[torch.Tensor], *,
                           nsplit: int, n_reqs: int, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int,
-                          scale: float, part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None) -> None:
+                          scale: float, part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
+                          single_rows: bool = False) -> None:
     """attention_talking on tensor cores for bfloat16 heads of 64 or 128 (keys and values of one width).  ``items`` int32
     [n_items, 6]: (request, first row within the request's rows of this step, rows (at most 16), first key, end of keys,
     partial slot or -1).  ``nsplit`` > 1: every request brings one row, cut into ``nsplit`` runs of keys whose partial sums
-    (slot = request * nsplit + run) a second kernel joins through ``part_o`` / ``part_ml`` (float32 scratch)."""
+    (slot = request * nsplit + run) a second kernel joins through ``part_o`` / ``part_ml`` (float32 scratch).
+    ``single_rows``: every item is one row (a step of single tokens); where its tiles fit, the kernel whose fragment rows
+    are the heads of a kv head's group runs instead of the one whose rows are tokens."""
     n = q.shape[0]
     _need(q.dtype == torch.bfloat16 and cache.dtype == q.dtype and out.dtype == q.dtype, "attention_talking_mma: bfloat16 only")
     _need(head_dim in TALKING_MMA_HEAD_DIMS and num_heads <= TALKING_MMA_MAX_HEADS, "attention_talking_mma: up to 16 heads of 64 or 128")
@@ -1518,8 +1521,8 @@ def attention_talking_mma(q: torch.Tensor, cache: torch.Tensor, out: torch.Tenso
         _dev(ctx_lens, "ctx_lens", torch.int32), _dev(block_table, "block_table", torch.int32), block_table.shape[1],
         _dev(mix, "mix", torch.float32), None if slope is None else _dev(slope, "slope", torch.float32),
         None if part_o is None else part_o.data_ptr(), None if part_ml is None else part_ml.data_ptr(), nsplit, n_reqs, num_heads,
-        num_kv_heads, head_dim, page_size, window, float(scale), cache.shape[0], status_tensor(q.device).data_ptr(), _stream()),
-        "attention_talking_mma")
+        num_kv_heads, head_dim, page_size, window, float(scale), cache.shape[0], status_tensor(q.device).data_ptr(),
+        1 if single_rows else 0, _stream()), "attention_talking_mma")
     if nsplit > 1:
         add_launches(1)
 

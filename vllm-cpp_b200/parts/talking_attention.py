@@ -161,7 +161,7 @@ class TalkingHeadsAttention(Mixer):
             ops.attention_talking_mma(q, pages, attn, gate, step.extras[key], step.shapes[key], step.q_start, step.ctx_lens, block_table,
                                       self.mix, self.slopes, nsplit=nsplit, n_reqs=step.n_reqs, num_heads=self.nh,
                                       num_kv_heads=self.nkv, head_dim=self.d, page_size=cache.page_size, window=self.window,
-                                      scale=self.scale, part_o=part_o, part_ml=part_ml)
+                                      scale=self.scale, part_o=part_o, part_ml=part_ml, single_rows=step.decode_only)
         else:
             ops.attention_talking(q, pages, attn, gate, step.positions, step.req_of_token, block_table, self.mix, self.slopes,
                                   window=self.window, scale=self.scale, **sizes)
