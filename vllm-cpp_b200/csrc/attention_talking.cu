@@ -183,7 +183,14 @@ struct TalkingMmaArgs {
     int bt_stride, H, G, page, window, num_pages;
     float scale;
     int* status;
+    int page_shift;             // log2(page) when the page size is a power of two, else -1
 };
+
+__device__ __forceinline__ uint32_t tkm_lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
 
 __device__ __forceinline__ void tkm_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -268,7 +275,7 @@ __global__ void __launch_bounds__(MAXT) attention_talking_mma_kernel(TalkingMmaA
             uint32_t bytes = 0;
             int sl = 0;
             if (j < k_hi) {
-                const int lp = j / a.page;
+                const int lp = a.page_shift >= 0 ? j >> a.page_shift : j / a.page;
                 sl = j - lp * a.page;
                 const int pg = lp < a.bt_stride ? bt[lp] : -1;
                 if ((unsigned)pg >= (unsigned)a.num_pages) {
@@ -462,11 +469,11 @@ __global__ void __launch_bounds__(MAXT) attention_talking_mma_kernel(TalkingMmaA
 // above), a warp per (kv head, sixteenth-of-a-tile): warp (g, ks) takes keys ks * 16 .. + 16 of every tile of 16 * KS keys
 // for the heads of group g, with sums of its own that the CTA joins at the end.  Raw scores of all heads meet in shared
 // memory as before; a warp mixes the rows of its own heads.
-template <int D, int MAXT>
-__global__ void __launch_bounds__(MAXT) attention_talking_decode_kernel(TalkingMmaArgs a, int KS) {
+template <int D, int KS, int MAXT>
+__global__ void __launch_bounds__(MAXT) attention_talking_decode_kernel(TalkingMmaArgs a) {
     constexpr int LDK = D + 8;
     extern __shared__ __align__(16) unsigned char tkm_smem[];
-    const int tile = 16 * KS;
+    constexpr int tile = 16 * KS;
     const size_t stage_elems = (size_t)a.G * tile * LDK;
     __nv_bfloat16* ks_ = reinterpret_cast<__nv_bfloat16*>(tkm_smem);               // [2][G][tile][LDK]
     __nv_bfloat16* vs_ = ks_ + 2 * stage_elems;                                     // [2][G][tile][LDK]
@@ -517,7 +524,7 @@ __global__ void __launch_bounds__(MAXT) attention_talking_decode_kernel(TalkingM
             uint32_t bytes = 0;
             int sl = 0;
             if (j < k_hi) {
-                const int lp = j / a.page;
+                const int lp = a.page_shift >= 0 ? j >> a.page_shift : j / a.page;
                 sl = j - lp * a.page;
                 const int pg = lp < a.bt_stride ? bt[lp] : -1;
                 if ((unsigned)pg >= (unsigned)a.num_pages) {
@@ -541,6 +548,9 @@ __global__ void __launch_bounds__(MAXT) attention_talking_decode_kernel(TalkingM
         asm volatile("cp.async.commit_group;\n" ::: "memory");
     };
 
+    // this lane's places in a stage: its key row of the warp's sixteen for the scores' B fragments, its row for ldmatrix
+    const uint32_t k_lane = cx_smem(ks_) + (uint32_t)((((g * tile + ks * 16) + gr) * LDK + tq * 2) * 2);
+    const uint32_t v_lane = cx_smem(vs_) + (uint32_t)((((g * tile + ks * 16) + (lane & 15)) * LDK) * 2);
     if (k_lo < k_hi) fetch(0, k_lo);
     int it = 0;
     for (int k0 = k_lo; k0 < k_hi; k0 += tile, ++it) {
@@ -548,9 +558,9 @@ __global__ void __launch_bounds__(MAXT) attention_talking_decode_kernel(TalkingM
         asm volatile("cp.async.wait_group 0;\n" ::: "memory");
         __syncthreads();
         if (k0 + tile < k_hi) fetch(st ^ 1, k0 + tile);
-        const __nv_bfloat16* kh = ks_ + (size_t)st * stage_elems + ((size_t)g * tile + ks * 16) * LDK;
-        const __nv_bfloat16* vh = vs_ + (size_t)st * stage_elems + ((size_t)g * tile + ks * 16) * LDK;
-        float* raw = raw0 + (size_t)st * a.H * tile;
+        const uint32_t stage_at = (uint32_t)st * (uint32_t)stage_elems * 2u;                 // bytes
+        const uint32_t kaddr = k_lane + stage_at, vaddr = v_lane + stage_at;
+        float* raw = raw0 + st * a.H * tile;
         float sc[2][4];
 #pragma unroll
         for (int n = 0; n < 2; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.0f;
@@ -558,8 +568,8 @@ __global__ void __launch_bounds__(MAXT) attention_talking_decode_kernel(TalkingM
         for (int s = 0; s < D / 16; ++s) {
 #pragma unroll
             for (int n = 0; n < 2; ++n) {
-                const __nv_bfloat16* kp = kh + (size_t)(n * 8 + gr) * LDK + s * 16 + tq * 2;
-                tkm_mma(sc[n], qf[s], *reinterpret_cast<const uint32_t*>(kp), *reinterpret_cast<const uint32_t*>(kp + 8));
+                const uint32_t kp = kaddr + (uint32_t)((n * 8 * LDK + s * 16) * 2);
+                tkm_mma(sc[n], qf[s], tkm_lds32(kp), tkm_lds32(kp + 16));
             }
         }
         // scale and distance bias; the rows of this group's heads into shared memory
@@ -578,9 +588,10 @@ __global__ void __launch_bounds__(MAXT) attention_talking_decode_kernel(TalkingM
         for (int n = 0; n < 2; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.0f;
         const float* wa = mixs + (size_t)(row_a ? head_a : 0) * a.H;
         const float* wb = mixs + (size_t)(row_b ? head_b : 0) * a.H;
-        for (int gg = 0; gg < a.H; ++gg) {
+        const float* theirs = raw + ks * 16 + tq * 2;
+#pragma unroll 4
+        for (int gg = 0; gg < a.H; ++gg, theirs += tile) {
             const float ua = wa[gg], ub = wb[gg];
-            const float* theirs = raw + (size_t)gg * tile + ks * 16 + tq * 2;
 #pragma unroll
             for (int n = 0; n < 2; ++n) {
                 const float2 r = *reinterpret_cast<const float2*>(theirs + n * 8);
@@ -637,11 +648,10 @@ __global__ void __launch_bounds__(MAXT) attention_talking_decode_kernel(TalkingM
         tkm_two_terms(sc[0][2], sc[0][3], hi[1], lo[1]);
         tkm_two_terms(sc[1][0], sc[1][1], hi[2], lo[2]);
         tkm_two_terms(sc[1][2], sc[1][3], hi[3], lo[3]);
-        const uint32_t vrow = cx_smem(vh + (size_t)(lane & 15) * LDK);
 #pragma unroll
         for (int n = 0; n < D / 8; ++n) {
             uint32_t b0, b1;
-            asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(b0), "=r"(b1) : "r"(vrow + n * 16));
+            asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(b0), "=r"(b1) : "r"(vaddr + n * 16));
             tkm_mma(o[n], hi, b0, b1);
             tkm_mma(o[n], lo, b0, b1);
         }
@@ -762,21 +772,26 @@ VCB_EXPORT int vcb_attention_talking_mma(const void* q, const void* cache, void*
     const long long smem = vcb_attention_talking_mma_smem(H, G, D);
     if (smem > 220 * 1024) return VCB_ERR_UNSUPPORTED;
     TalkingMmaArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, (const __nv_bfloat16*)gate, ldg, items,
-                     q_start, ctx_lens, block_table, mix, slope, part_o, part_ml, bt_stride, H, G, page, window, num_pages, scale, status};
+                     q_start, ctx_lens, block_table, mix, slope, part_o, part_ml, bt_stride, H, G, page, window, num_pages, scale, status,
+                     (page & (page - 1)) ? -1 : __builtin_ctz((unsigned)page)};
     cudaStream_t s = (cudaStream_t)stream;
     long long dsmem = 0;
     const int KS = single_rows ? tkm_decode_split(H, G, D, &dsmem) : 0;
     if (KS) {
-        static unsigned long long ddone[2] = {0, 0};
-        if (D == 64) {
-            const int e = vcb_allow_dynamic_smem(attention_talking_decode_kernel<64, 512>, 200 * 1024, &ddone[0]);
-            if (e) return e;
-            vcb_launch(attention_talking_decode_kernel<64, 512>, n_items, G * KS * 32, (size_t)dsmem, s, a, KS);
-        } else {
-            const int e = vcb_allow_dynamic_smem(attention_talking_decode_kernel<128, 256>, 200 * 1024, &ddone[1]);
-            if (e) return e;
-            vcb_launch(attention_talking_decode_kernel<128, 256>, n_items, G * KS * 32, (size_t)dsmem, s, a, KS);
-        }
+        static unsigned long long ddone[6] = {0, 0, 0, 0, 0, 0};
+#define TKD_GO(DD, KK, TT, I)                                                                                       \
+    do {                                                                                                            \
+        const int e = vcb_allow_dynamic_smem(attention_talking_decode_kernel<DD, KK, TT>, 200 * 1024, &ddone[I]);   \
+        if (e) return e;                                                                                            \
+        vcb_launch(attention_talking_decode_kernel<DD, KK, TT>, n_items, G * KK * 32, (size_t)dsmem, s, a);         \
+    } while (0)
+        if (D == 64 && KS == 4) TKD_GO(64, 4, 512, 0);
+        else if (D == 64 && KS == 2) TKD_GO(64, 2, 512, 1);
+        else if (D == 64) TKD_GO(64, 1, 512, 2);
+        else if (KS == 4) TKD_GO(128, 4, 256, 3);
+        else if (KS == 2) TKD_GO(128, 2, 256, 4);
+        else TKD_GO(128, 1, 256, 5);
+#undef TKD_GO
         if (nsplit > 1)
             vcb_launch(attention_talking_merge_kernel, n_reqs, H * 32, 0, s, (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out,
                        (const __nv_bfloat16*)gate, ldg, q_start, H, D, nsplit);
