@@ -474,11 +474,13 @@ __global__ void __launch_bounds__(MAXT) attention_talking_decode_kernel(TalkingM
     constexpr int LDK = D + 8;
     extern __shared__ __align__(16) unsigned char tkm_smem[];
     constexpr int tile = 16 * KS;
+    constexpr int RS = tile + 8;                    // floats between two heads' raw scores: eight heads' pairs fall into eight banks
+    const int MS = a.H | 1;                         // floats between two rows of the mixing matrix: odd, so that rows fall into different banks
     const size_t stage_elems = (size_t)a.G * tile * LDK;
     __nv_bfloat16* ks_ = reinterpret_cast<__nv_bfloat16*>(tkm_smem);               // [2][G][tile][LDK]
     __nv_bfloat16* vs_ = ks_ + 2 * stage_elems;                                     // [2][G][tile][LDK]
-    float* raw0 = reinterpret_cast<float*>(vs_ + 2 * stage_elems);                 // [2][H][tile]
-    float* mixs = raw0 + 2 * (size_t)a.H * tile;                                    // [H][H], times log2(e)
+    float* raw0 = reinterpret_cast<float*>(vs_ + 2 * stage_elems);                 // [2][H][RS]
+    float* mixs = raw0 + 2 * (size_t)a.H * RS;                                      // [H][MS], times log2(e)
     pdl_start();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = warp / KS, ks = warp - g * KS;
@@ -489,7 +491,7 @@ __global__ void __launch_bounds__(MAXT) attention_talking_decode_kernel(TalkingM
     const int row = a.q_start[req] + item[1];
     const int pos = a.ctx_lens[req] + item[1];
     const int* bt = a.block_table + (size_t)req * a.bt_stride;
-    for (int i = threadIdx.x; i < a.H * a.H; i += blockDim.x) mixs[i] = a.mix[i] * 1.4426950408889634f;
+    for (int i = threadIdx.x; i < a.H * a.H; i += blockDim.x) mixs[(i / a.H) * MS + i % a.H] = a.mix[i] * 1.4426950408889634f;
     const bool row_a = gr < Hg, row_b = gr + 8 < Hg;
     const int head_a = g * Hg + gr, head_b = head_a + 8;
     const float slope_a = (a.slope && row_a) ? a.slope[head_a] : 0.0f, slope_b = (a.slope && row_b) ? a.slope[head_b] : 0.0f;
@@ -560,7 +562,7 @@ __global__ void __launch_bounds__(MAXT) attention_talking_decode_kernel(TalkingM
         if (k0 + tile < k_hi) fetch(st ^ 1, k0 + tile);
         const uint32_t stage_at = (uint32_t)st * (uint32_t)stage_elems * 2u;                 // bytes
         const uint32_t kaddr = k_lane + stage_at, vaddr = v_lane + stage_at;
-        float* raw = raw0 + st * a.H * tile;
+        float* raw = raw0 + st * a.H * RS;
         float sc[2][4];
 #pragma unroll
         for (int n = 0; n < 2; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.0f;
@@ -577,20 +579,20 @@ __global__ void __launch_bounds__(MAXT) attention_talking_decode_kernel(TalkingM
 #pragma unroll
         for (int n = 0; n < 2; ++n) {
             const float da = (float)(pos - j0 - n * 8);
-            if (row_a) *reinterpret_cast<float2*>(raw + (size_t)head_a * tile + ks * 16 + n * 8 + tq * 2) =
+            if (row_a) *reinterpret_cast<float2*>(raw + head_a * RS + ks * 16 + n * 8 + tq * 2) =
                 make_float2(fmaf(sc[n][0], a.scale, -slope_a * da), fmaf(sc[n][1], a.scale, -slope_a * (da - 1.0f)));
-            if (row_b) *reinterpret_cast<float2*>(raw + (size_t)head_b * tile + ks * 16 + n * 8 + tq * 2) =
+            if (row_b) *reinterpret_cast<float2*>(raw + head_b * RS + ks * 16 + n * 8 + tq * 2) =
                 make_float2(fmaf(sc[n][2], a.scale, -slope_b * da), fmaf(sc[n][3], a.scale, -slope_b * (da - 1.0f)));
         }
         __syncthreads();
         // the mixed scores of this warp's heads at its sixteen keys, in units of log 2
 #pragma unroll
         for (int n = 0; n < 2; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.0f;
-        const float* wa = mixs + (size_t)(row_a ? head_a : 0) * a.H;
-        const float* wb = mixs + (size_t)(row_b ? head_b : 0) * a.H;
+        const float* wa = mixs + (row_a ? head_a : 0) * MS;
+        const float* wb = mixs + (row_b ? head_b : 0) * MS;
         const float* theirs = raw + ks * 16 + tq * 2;
 #pragma unroll 4
-        for (int gg = 0; gg < a.H; ++gg, theirs += tile) {
+        for (int gg = 0; gg < a.H; ++gg, theirs += RS) {
             const float ua = wa[gg], ub = wb[gg];
 #pragma unroll
             for (int n = 0; n < 2; ++n) {
@@ -711,7 +713,7 @@ static int tkm_decode_split(int H, int G, int D, long long* smem_out) {
     for (int KS = 4; KS >= 1; KS >>= 1) {
         if (G * KS > most_warps) continue;
         const long long tiles = (long long)4 * G * 16 * KS * (D + 8) * 2, join = (long long)G * KS * 16 * (D + 2) * 4;
-        const long long smem = (tiles > join ? tiles : join) + (long long)2 * H * 16 * KS * 4 + (long long)H * H * 4;
+        const long long smem = (tiles > join ? tiles : join) + (long long)2 * H * (16 * KS + 8) * 4 + (long long)H * (H | 1) * 4;
         if (smem <= 200 * 1024) { *smem_out = smem; return KS; }
     }
     return 0;
