@@ -1262,7 +1262,7 @@ def gipinex_configs(size):
     layers = [{"type": "latent_attention", "mixer": lat, "mlp": dense}, {"type": "latent_attention", "mixer": lat, "mlp": moe},
               {"type": "attention", "mixer": att, "mlp": moe}, {"type": "attention", "mixer": att, "mlp": moe}]
     loop = {"start": 0, "stop": 2, "times": 2}
-    gipinex = {"architecture": "Gipinex", "vocab": GIPINEX_VOCAB, "width": w, "norm": {"eps": 1e-6}, "residual_mult": 0.7,
+    gipinex = {"architecture": "Gipinex", "vocab": GIPINEX_VOCAB, "width": w, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
                "loop": loop, "layers": [layers[i % 4] for i in range(z["layers"])]}
     l_moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"], "scale": 2.5}}
     l_att = {"heads": h, "kv_heads": z["kv_heads"], "dim": d, "vdim": d, "scale": d ** -0.5, "rot": {"base": 1e6, "dims": d // 2}}
@@ -1414,11 +1414,11 @@ def gipinex_kernels(z, peaks):
         add(f"Qwen2: silu(gate) * up, width {ff}, {t} tokens", "like the one above", lambda i: ops.silu_mul(gu[i % c], act[i % c]), c, bytes_=t * ff * 6)
         x = [rnd(t, h, dtype=torch.float32) for _ in range(c)]
         dl, pair = [rnd(t, h) for _ in range(c)], [torch.empty(t, 2 * h, dtype=bf, device=dev) for _ in range(c)]
-        add(f"stream + 0.7 * addition into the left half of the re-making product's input, {t} tokens", "", lambda i: ops.cast_rows(
-            x[i % c], dl[i % c], 0.7, pair[i % c][:, :h]), c, bytes_=t * h * 8)
+        add(f"stream + 0.5 * addition into the left half of the re-making product's input, {t} tokens", "", lambda i: ops.cast_rows(
+            x[i % c], dl[i % c], 0.5, pair[i % c][:, :h]), c, bytes_=t * h * 8)
         nrm, gh = [torch.empty(t, h, dtype=bf, device=dev) for _ in range(c)], torch.ones(h, device=dev)
-        add(f"stream += 0.7 * addition, then the norm, {t} tokens", "the kernel Qwen2 runs with factor 1", lambda i: ops.add_rmsnorm(
-            x[i % c], dl[i % c], gh, nrm[i % c], 1e-6, None, 0.7), c, bytes_=t * h * 12)
+        add(f"stream += 0.5 * addition, then the norm, {t} tokens", "the kernel Qwen2 runs with factor 1", lambda i: ops.add_rmsnorm(
+            x[i % c], dl[i % c], gh, nrm[i % c], 1e-6, None, 0.5), c, bytes_=t * h * 12)
     ops.check_status()
     return rows
 

@@ -8,7 +8,7 @@ stream is re-made from itself and the embedding output x0:  x <- W_in [x ; x0]. 
 stream times the embedding table.  Mixers:
 
   "attention"         grouped-query softmax attention without rotation and without a value projection: the values are
-                      the keys as projected, while scores are taken between q and k divided by their root mean square
+                      the unnormed key projection, while scores are taken between q and k divided by their root mean square
                       per head.  A score is scale * q_i . k_j - slope_h * (i - j) with slope_h = 2^(-8 (h + 1) / H); the
                       scores of the H heads at (i, j) are then mixed by an H x H matrix before the softmax.  The
                       concatenated heads are gated coordinate by coordinate by sigmoid(W_g x).
@@ -227,7 +227,7 @@ def talking_attention(h, weights, p, m, eps):
     G = m.get("kv_heads") or H
     q = (h @ weights[p + "q"].T).reshape(n, H, d)
     k = (h @ weights[p + "k"].T).reshape(n, G, d)
-    v = k                                           # the values are the keys as projected
+    v = k                                           # the unnormed key projection doubles as the value
     qn, kn = rms(q, eps), rms(k, eps)
     pos = np.arange(n)
     dist = pos[:, None] - pos[None, :]              # i - j

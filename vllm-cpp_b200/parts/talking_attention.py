@@ -2,7 +2,7 @@
 rotation and without a value projection:
 
     q = W_q h,  k = W_k h                            heads of ``head_dim``; query head g reads kv head g // (heads / kv_heads)
-    v = k                                            the values are the keys as projected
+    v = k                                            the unnormed key projection doubles as the value
     qn, kn = q, k divided by their root mean square per head (eps inside the root; no gain)
     raw_g(i, j) = scale * (qn_i,g . kn_j) - slope_g * (i - j),   slope_g = 2^(-slope_span * (g + 1) / heads)
     s_h(i, j)   = sum_g talk[h, g] * raw_g(i, j)     the heads' scores mixed by a learned heads x heads matrix
@@ -10,7 +10,7 @@ rotation and without a value projection:
 
 ``slope_span`` 0 switches the distance bias off, ``talk`` False the mixing (the identity is used), ``qk_norm`` False
 the division, ``output_gate`` False the gate; ``window`` > 0 restricts a query to the last ``window`` keys.  The cache
-holds the normed keys in its key plane and the keys as projected in its value plane.  q, k and the gate are one product;
+holds the normed keys in its key plane and the unnormed key projection in its value plane.  q, k and the gate are one product;
 the norms and the cache write are the kernel that attention with head norms uses (csrc/attention_biased.cu,
 qk_head_rope_cache_write_kernel with a gain of ones and no rotation); attention is csrc/attention_talking.cu: in
 bfloat16 with up to 16 heads of 64 or 128 the tensor-core kernel over work items that the host lists per step (16 query
@@ -145,7 +145,7 @@ class TalkingHeadsAttention(Mixer):
         pages = cache.pages.view(cache.pages.shape[0], -1)
         sizes = dict(num_heads=self.nh, num_kv_heads=self.nkv, head_dim=self.d, v_head_dim=self.d, row=self.d, page_size=cache.page_size)
         q = ws.take((n, self.nh * self.d), self.dtype)
-        # keys normed per head into the key plane, the same keys as projected into the value plane
+        # keys normed per head into the key plane, the same keys, unnormed, into the value plane
         ops.qk_head_rope_cache_write(proj, 0, k_off, k_off, self.ones, self.ones, None, q, pages, step.positions, step.req_of_token,
                                      block_table, eps=self.eps, write_kv=writes_cache, **sizes)
         attn = ws.take((n, self.nh * self.d), self.dtype)
