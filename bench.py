@@ -1338,11 +1338,15 @@ def gipinex_kernels(z, peaks):
     q, o, gate = rnd(t, nh * d), torch.empty(t, nh * d, dtype=bf, device=dev), rnd(t, nh * d)
     kv = rnd(n_pages, 2 * nkv * page * d, scale=0.5)
     host = HostStep([t], [0], page)
-    items = torch.from_numpy(talk.step_arrays()[talk._items_key()](host)).to(dev)
+    lists = talk.step_arrays()
+    items = torch.from_numpy(lists[talk._items_key()](host)).to(dev)
+    joins = torch.from_numpy(lists[talk._items_key() + "_joins"](host)).to(dev)       # tiles cut along their keys, joined by a second kernel
+    wide = talk.max_wide_slots() * ops.TALKING_ITEM_ROWS * nh
+    wo, wml = torch.empty(wide * d, device=dev), torch.empty(wide * 2, device=dev)
     seen = t * (t + 1) // 2
     add(f"attention with talking heads, distance bias, gate and two-term weights, prompt of {t}", "", lambda i: ops.attention_talking_mma(
         q, kv, o, gate, items, items.shape[0], q_start, ctx, bt, mix, slopes, nsplit=1, n_reqs=1, num_heads=nh, num_kv_heads=nkv, head_dim=d,
-        page_size=page, window=0, scale=0.125), 4, flops=4.0 * nh * d * seen)
+        page_size=page, window=0, scale=0.125, part_o=wo, part_ml=wml, merge=joins, n_merge=joins.shape[0]), 4, flops=4.0 * nh * d * seen)
     G = nh // nkv
     n_tiles = -(-t * G // ops.TC_ATTENTION_TILE_ROWS)
     tile_req = torch.zeros(n_tiles, dtype=torch.int32, device=dev)

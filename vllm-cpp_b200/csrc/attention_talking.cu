@@ -16,8 +16,11 @@
 //                                   head; per tile of 32 keys every warp takes its head's 16 x 32 raw scores, leaves them
 //                                   in shared memory, mixes its own row of the heads' matrix from there in float, runs the
 //                                   online softmax on its fragments and multiplies the weights, as two bfloat16 terms
-//                                   (16 bits of mantissa), with the value tile.  A work item that holds only part of a
-//                                   row's keys leaves (o, m, l) partials; attention_talking_merge_kernel joins them.
+//                                   (16 bits of mantissa), with the value tile.  A work item that holds only part of its
+//                                   rows' keys leaves (o, m, l) partials; attention_talking_merge_rows_kernel joins them.
+//   attention_talking_decode_kernel the same for requests that bring one token: the fragment's rows are the heads of a kv
+//                                   head's group, a warp per (kv head, sixteen keys of a tile); the runs of a request's
+//                                   keys leave partials that attention_talking_merge_kernel joins.
 //
 // The reference's attention (src/attention/paged_attention.cu) has independent heads.
 #include "common.cuh"
@@ -164,6 +167,7 @@ VCB_EXPORT int vcb_attention_talking(const void* q, const void* cache, void* out
 #define TKM_ROWS 16            // query rows of a work item
 #define TKM_KEYS 32            // keys of a tile
 #define TKM_MAX_HEADS 16       // a warp per head, and a head's fragments want more registers than 1024 threads leave
+#define TKM_MAX_PARTS 8        // most items a portion's tile is cut into along its keys
 #define TKM_ITEM_INTS 6        // request, first row within the request's rows of this step, rows, first key, end of keys, partial slot or -1
 
 struct TalkingMmaArgs {
@@ -184,6 +188,7 @@ struct TalkingMmaArgs {
     float scale;
     int* status;
     int page_shift;             // log2(page) when the page size is a power of two, else -1
+    int wide;                   // 1: an item's partial sums are kept for all its 16 rows, [slot][head][row][D] (portions cut along the keys)
 };
 
 __device__ __forceinline__ uint32_t tkm_lds32(uint32_t addr) {
@@ -428,6 +433,23 @@ __global__ void __launch_bounds__(MAXT) attention_talking_mma_kernel(TalkingMmaA
                 tkm_mma(o[n], lo, b0, b1);
             }
         }
+    }
+    if (slot_out >= 0 && a.wide) {
+        // part of the keys of a portion's rows: every row's sums as they stand, with their references and weights
+        float* po = a.part_o + ((size_t)slot_out * a.H + h) * TKM_ROWS * D;
+        float* pm = a.part_ml + ((size_t)slot_out * a.H + h) * TKM_ROWS * 2;
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n) {
+            *reinterpret_cast<float2*>(po + (size_t)gr * D + n * 8 + tq * 2) = make_float2(o[n][0], o[n][1]);
+            *reinterpret_cast<float2*>(po + (size_t)(gr + 8) * D + n * 8 + tq * 2) = make_float2(o[n][2], o[n][3]);
+        }
+        if (tq == 0) {
+            pm[gr * 2] = m_a;
+            pm[gr * 2 + 1] = l_a;
+            pm[(gr + 8) * 2] = m_b;
+            pm[(gr + 8) * 2 + 1] = l_b;
+        }
+        return;
     }
     if (slot_out >= 0) {
         // part of a row's keys (single rows only): the sums as they stand, with their reference and weight
@@ -754,18 +776,62 @@ __global__ void attention_talking_merge_kernel(const float* __restrict__ part_o,
     }
 }
 
+// Joins the partial sums of portions that were cut along the keys.  merge: [n, 5] = (request, first row within the request's
+// rows of this step, rows, first slot, slots); partials as the kernel above leaves them with `wide`.  A CTA per entry, a
+// warp per head.
+__global__ void attention_talking_merge_rows_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                                    __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gate, long long ldg,
+                                                    const int* __restrict__ q_start, const int* __restrict__ merge, int H, int D) {
+    pdl_start();
+    const int* e = merge + (size_t)blockIdx.x * 5;
+    const int r = blockIdx.y;                       // a row of the entry a CTA, a warp per head
+    if (r >= e[2]) return;
+    const int row = q_start[e[0]] + e[1] + r, first = e[3], parts = min(e[4], TKM_MAX_PARTS);
+    const int h = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (h >= H) return;
+    float ms[TKM_MAX_PARTS], ls[TKM_MAX_PARTS];
+#pragma unroll
+    for (int s = 0; s < TKM_MAX_PARTS; ++s) {       // every load in flight at once
+        const float2 v = s < parts ? *reinterpret_cast<const float2*>(part_ml + (((size_t)(first + s) * H + h) * TKM_ROWS + r) * 2)
+                                   : make_float2(-INFINITY, 0.0f);
+        ms[s] = v.x;
+        ls[s] = v.y;
+    }
+    float m = -INFINITY;
+#pragma unroll
+    for (int s = 0; s < TKM_MAX_PARTS; ++s) m = fmaxf(m, ms[s]);
+    float l = 0.0f;
+#pragma unroll
+    for (int s = 0; s < TKM_MAX_PARTS; ++s) {
+        ms[s] = ms[s] == -INFINITY ? 0.0f : exp2f(ms[s] - m);        // from here on the part's factor
+        l = fmaf(ls[s], ms[s], l);
+    }
+    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+    for (int i = lane; i < D; i += 32) {
+        float acc = 0.0f;
+#pragma unroll
+        for (int s = 0; s < TKM_MAX_PARTS; ++s)
+            if (s < parts) acc = fmaf(part_o[(((size_t)(first + s) * H + h) * TKM_ROWS + r) * D + i], ms[s], acc);
+        float y = acc * inv;
+        if (gate) y *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)row * ldg + (size_t)h * D + i])));
+        out[((size_t)row * H + h) * D + i] = __float2bfloat16_rn(y);
+    }
+}
+
 VCB_EXPORT long long vcb_attention_talking_mma_smem(int H, int G, int D) {
     return (long long)4 * G * TKM_KEYS * (D + 8) * 2 + (long long)2 * H * TKM_ROWS * TKM_KEYS * 4 + (long long)H * H * 4;
 }
 
 // items: [n_items, 6] as TalkingMmaArgs says.  nsplit > 1: every item is one row of a request cut into nsplit runs
 // (slot = request * nsplit + run), and the merge kernel writes the n_reqs rows.  single_rows 1: every item is one row
-// (a step of single tokens), which the kernel whose fragment rows are heads takes where its tiles fit.
+// (a step of single tokens), which the kernel whose fragment rows are heads takes where its tiles fit.  merge (n_merge
+// entries of 5, see attention_talking_merge_rows_kernel): portions whose keys were cut into several items, each with a slot.
 VCB_EXPORT int vcb_attention_talking_mma(const void* q, const void* cache, void* out, const void* gate, long long ldg,
                                          const int* items, int n_items, const int* q_start, const int* ctx_lens,
                                          const int* block_table, int bt_stride, const float* mix, const float* slope,
                                          float* part_o, float* part_ml, int nsplit, int n_reqs, int H, int G, int D, int page,
-                                         int window, float scale, int num_pages, int* status, int single_rows, void* stream) {
+                                         int window, float scale, int num_pages, int* status, int single_rows, const int* merge,
+                                         int n_merge, void* stream) {
     if (n_items <= 0) return 0;
     if (!q || !cache || !out || !items || !mix || H <= 0 || G <= 0 || H % G || page <= 0 || window < 0 || num_pages < 0 || nsplit < 1)
         return VCB_ERR_BAD_ARG;
@@ -775,7 +841,8 @@ VCB_EXPORT int vcb_attention_talking_mma(const void* q, const void* cache, void*
     if (smem > 220 * 1024) return VCB_ERR_UNSUPPORTED;
     TalkingMmaArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, (const __nv_bfloat16*)gate, ldg, items,
                      q_start, ctx_lens, block_table, mix, slope, part_o, part_ml, bt_stride, H, G, page, window, num_pages, scale, status,
-                     (page & (page - 1)) ? -1 : __builtin_ctz((unsigned)page)};
+                     (page & (page - 1)) ? -1 : __builtin_ctz((unsigned)page), (merge && n_merge > 0) ? 1 : 0};
+    if (a.wide && (nsplit > 1 || single_rows || !part_o || !part_ml)) return VCB_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     long long dsmem = 0;
     const int KS = single_rows ? tkm_decode_split(H, G, D, &dsmem) : 0;
@@ -811,6 +878,9 @@ VCB_EXPORT int vcb_attention_talking_mma(const void* q, const void* cache, void*
     else if (H <= 8) TKM_GO(128, 256, 2);
     else TKM_GO(128, 512, 3);
 #undef TKM_GO
+    if (a.wide)
+        vcb_launch(attention_talking_merge_rows_kernel, dim3(n_merge, TKM_ROWS), H * 32, 0, s, (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out,
+                   (const __nv_bfloat16*)gate, ldg, q_start, merge, H, D);
     if (nsplit > 1)
         vcb_launch(attention_talking_merge_kernel, n_reqs, H * 32, 0, s, (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out,
                    (const __nv_bfloat16*)gate, ldg, q_start, H, D, nsplit);

@@ -61,7 +61,7 @@ _SIGNATURES = {
     "vcb_clamped_swish_mul": [_P, _P, _P, _I, _I, _F, _F, _F, _I, _P],
     "vcb_moe_router_biased": [_P, _L, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P],
     "vcb_moe_combine_add": [_P, _P, _L, _P, _P, _P, _I, _I, _I, _P, _L, _I, _P],
-    "vcb_attention_talking_mma": [_P, _P, _P, _P, _L, _P, _I, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _I, _P],
+    "vcb_attention_talking_mma": [_P, _P, _P, _P, _L, _P, _I, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _I, _P, _I, _P],
     "vcb_attention_talking": [_P, _P, _P, _P, _L, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _I, _P],
     "vcb_attention_decode_mma_shaped_planes": [_P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _I, _F, _P, _I,
                                                _P, _P, _L, _I, _I, _P],
@@ -1479,6 +1479,7 @@ TALKING_ITEM_ROWS = 16             # query rows of a work item of the tensor-cor
 TALKING_KEY_TILE = 32
 TALKING_MAX_SPLITS = 32
 TALKING_ITEM_INTS = 6
+TALKING_MAX_PARTS = 8              # most items a portion's tile is cut into along its keys
 
 
 def talking_mma_fits(num_heads: int, num_kv_heads: int, head_dim: int) -> bool:
@@ -1495,13 +1496,15 @@ def attention_talking_mma(q: torch.Tensor, cache: torch.Tensor, out: torch.Tenso
                           n_items: int, q_start, ctx_lens, block_table, mix: torch.Tensor, slope: Optional[torch.Tensor], *,
                           nsplit: int, n_reqs: int, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int,
                           scale: float, part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
-                          single_rows: bool = False) -> None:
+                          single_rows: bool = False, merge: Optional[torch.Tensor] = None, n_merge: int = 0) -> None:
     """attention_talking on tensor cores for bfloat16 heads of 64 or 128 (keys and values of one width).  ``items`` int32
     [n_items, 6]: (request, first row within the request's rows of this step, rows (at most 16), first key, end of keys,
     partial slot or -1).  ``nsplit`` > 1: every request brings one row, cut into ``nsplit`` runs of keys whose partial sums
     (slot = request * nsplit + run) a second kernel joins through ``part_o`` / ``part_ml`` (float32 scratch).
     ``single_rows``: every item is one row (a step of single tokens); where its tiles fit, the kernel whose fragment rows
-    are the heads of a kv head's group runs instead of the one whose rows are tokens."""
+    are the heads of a kv head's group runs instead of the one whose rows are tokens.  ``merge`` int32 [n_merge, 5]: portions
+    whose keys were cut into several items (request, first row, rows, first slot, slots); their partial sums, kept for
+    all 16 rows of an item (scratch of slots * heads * 16 * (head_dim + 2) floats), are joined by a second kernel."""
     n = q.shape[0]
     _need(q.dtype == torch.bfloat16 and cache.dtype == q.dtype and out.dtype == q.dtype, "attention_talking_mma: bfloat16 only")
     _need(head_dim in TALKING_MMA_HEAD_DIMS and num_heads <= TALKING_MMA_MAX_HEADS, "attention_talking_mma: up to 16 heads of 64 or 128")
@@ -1515,6 +1518,9 @@ def attention_talking_mma(q: torch.Tensor, cache: torch.Tensor, out: torch.Tenso
         need = n_reqs * nsplit * num_heads
         _need(part_o is not None and part_ml is not None and part_o.numel() >= need * head_dim and part_ml.numel() >= need * 2,
               "attention_talking_mma: scratch for the partial sums")
+    if n_merge:
+        _need(merge is not None and merge.dtype == torch.int32 and merge.is_contiguous() and merge.numel() >= n_merge * 5 and nsplit == 1
+              and part_o is not None and part_ml is not None, "attention_talking_mma: merge entries with their scratch")
     _check(lib().vcb_attention_talking_mma(
         _dev(q, "q"), _dev(cache, "cache"), _dev(out, "out"), None if gate is None else gate.data_ptr(),
         0 if gate is None else gate.stride(0), items.data_ptr(), n_items, _dev(q_start, "q_start", torch.int32),
@@ -1522,8 +1528,8 @@ def attention_talking_mma(q: torch.Tensor, cache: torch.Tensor, out: torch.Tenso
         _dev(mix, "mix", torch.float32), None if slope is None else _dev(slope, "slope", torch.float32),
         None if part_o is None else part_o.data_ptr(), None if part_ml is None else part_ml.data_ptr(), nsplit, n_reqs, num_heads,
         num_kv_heads, head_dim, page_size, window, float(scale), cache.shape[0], status_tensor(q.device).data_ptr(),
-        1 if single_rows else 0, _stream()), "attention_talking_mma")
-    if nsplit > 1:
+        1 if single_rows else 0, merge.data_ptr() if n_merge else None, n_merge, _stream()), "attention_talking_mma")
+    if nsplit > 1 or n_merge:
         add_launches(1)
 
 

@@ -83,17 +83,22 @@ class TalkingHeadsAttention(Mixer):
     SPLIT_LADDER = (1, 2, 3, 4, 6, 8, 12, 16, 24, 32)
 
     def step_arrays(self):
-        """Work items of the tensor-core kernel, [items, 6] int32 (ops.attention_talking_mma): portions in tiles of 16
-        rows, the tiles that see the most keys first; a step of single tokens with every request's keys cut into as
-        many runs (the same number for all, from a short ladder) as fill the device once with two CTAs an SM, a run
-        being at least four key tiles.  The number of items and of runs are launch shapes of the step."""
+        """Work items of the tensor-core kernel, [items, 6] int32 (ops.attention_talking_mma).  Portions: tiles of 16 rows;
+        a tile that sees many more keys than a CTA's fair share of the step (causal work is triangular) is cut along its
+        keys into items of equal runs, each with a slot for its partial sums, and listed in a second array
+        [entries, 5] = (request, first row, rows, first slot, slots) for the kernel that joins them; the items that see the
+        most keys go first.  A step of single tokens: every request's keys cut into as many runs (the same number for
+        all, from a short ladder) as fill the device once with two CTAs an SM, a run being at least four key tiles.  The
+        numbers of items, runs and entries are launch shapes of the step."""
         if not self._tensor_core_path():
             return {}
         key = self._items_key()
 
-        def items(host):
+        def plan(host):
+            if getattr(host, "_talk_plan", None) is not None and host._talk_plan[0] == key:
+                return host._talk_plan[1:]
             rows, tile = ops.TALKING_ITEM_ROWS, ops.TALKING_KEY_TILE
-            out = []
+            out, merges = [], []
             if all(q == 1 for q in host.q_lens):
                 hi = [c + 1 for c in host.ctx_lens]
                 lo = [max(0, h - self.window) if self.window > 0 else 0 for h in hi]
@@ -107,21 +112,48 @@ class TalkingHeadsAttention(Mixer):
                         out.append((r, 0, 1, a, b, r * nsplit + s if nsplit > 1 else -1))
             else:
                 nsplit = 1
+                whole = []
                 for r, (q, ctx) in enumerate(zip(host.q_lens, host.ctx_lens)):
                     for q0 in range(0, q, rows):
                         nq = min(rows, q - q0)
                         k_lo = max(0, ctx + q0 - self.window + 1) if self.window > 0 else 0
-                        out.append((r, q0, nq, k_lo, ctx + q0 + nq, -1))
+                        whole.append((r, q0, nq, k_lo, ctx + q0 + nq))
+                tiles = [-(-(it[4] - it[3]) // tile) for it in whole]
+                share = max(8, -(-sum(tiles) // ops.sm_count()))                # key tiles of a CTA if all had the same
+                slots = 0
+                for it, n in zip(whole, tiles):
+                    parts = min(ops.TALKING_MAX_PARTS, -(-n // share)) if n > share + share // 4 else 1
+                    if parts == 1 or slots + parts > self.max_wide_slots():
+                        out.append(it + (-1,))
+                        continue
+                    per = -(-n // parts) * tile
+                    for s in range(parts):
+                        out.append((it[0], it[1], it[2], min(it[4], it[3] + s * per), min(it[4], it[3] + (s + 1) * per), slots + s))
+                    merges.append((it[0], it[1], it[2], slots, parts))
+                    slots += parts
                 out.sort(key=lambda it: it[3] - it[4])                        # the longest first (a stable sort)
+            host._talk_plan = (key, out, merges, nsplit)
+            return out, merges, nsplit
+
+        def items(host):
+            out, merges, nsplit = plan(host)
             host.shapes[key] = len(out)
             host.shapes[key + "_runs"] = nsplit
+            host.shapes[key + "_joins"] = len(merges)
             return np.asarray(out, dtype=np.int32).reshape(-1, ops.TALKING_ITEM_INTS)
 
-        return {key: items}
+        def joins(host):
+            return np.asarray(plan(host)[1], dtype=np.int32).reshape(-1, 5)
+
+        return {key: items, key + "_joins": joins}
+
+    def max_wide_slots(self) -> int:
+        """Most slots for partial sums of portions cut along their keys (each holds 16 rows of every head)."""
+        return 2 * ops.sm_count()
 
     def reserve(self, n_tokens, n_reqs, device):
         if self._tensor_core_path():
-            most = n_reqs * ops.TALKING_MAX_SPLITS * self.nh
+            most = max(n_reqs * ops.TALKING_MAX_SPLITS, self.max_wide_slots() * ops.TALKING_ITEM_ROWS) * self.nh
             ops.scratch("talk_part_o", most * self.d, device)
             ops.scratch("talk_part_ml", most * 2, device)
 
@@ -153,15 +185,17 @@ class TalkingHeadsAttention(Mixer):
         key = self._items_key()
         if self._tensor_core_path() and key in step.extras and key in step.shapes:
             nsplit = step.shapes[key + "_runs"]
+            n_joins = step.shapes.get(key + "_joins", 0)
             part_o = part_ml = None
-            if nsplit > 1:
-                need = step.n_reqs * nsplit * self.nh
+            if nsplit > 1 or n_joins:
+                need = max(step.n_reqs * nsplit, self.max_wide_slots() * ops.TALKING_ITEM_ROWS if n_joins else 0) * self.nh
                 part_o = ops.scratch("talk_part_o", need * self.d, q.device)
                 part_ml = ops.scratch("talk_part_ml", need * 2, q.device)
             ops.attention_talking_mma(q, pages, attn, gate, step.extras[key], step.shapes[key], step.q_start, step.ctx_lens, block_table,
                                       self.mix, self.slopes, nsplit=nsplit, n_reqs=step.n_reqs, num_heads=self.nh,
                                       num_kv_heads=self.nkv, head_dim=self.d, page_size=cache.page_size, window=self.window,
-                                      scale=self.scale, part_o=part_o, part_ml=part_ml, single_rows=step.decode_only)
+                                      scale=self.scale, part_o=part_o, part_ml=part_ml, single_rows=step.decode_only,
+                                      merge=step.extras.get(key + "_joins") if n_joins else None, n_merge=n_joins)
         else:
             ops.attention_talking(q, pages, attn, gate, step.positions, step.req_of_token, block_table, self.mix, self.slopes,
                                   window=self.window, scale=self.scale, **sizes)
